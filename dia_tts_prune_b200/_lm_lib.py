@@ -11,12 +11,13 @@ from pathlib import Path
 
 from . import build as _build
 
-MIXER_SINK_ATTENTION, MIXER_TALK_ATTENTION, MIXER_HGRN2, MIXER_CHANNEL_DELTA = 1, 2, 3, 4
+MIXER_SINK_ATTENTION, MIXER_TALK_ATTENTION, MIXER_HGRN2, MIXER_CHANNEL_DELTA, MIXER_LATENT_ATTENTION, MIXER_MLSTM = 1, 2, 3, 4, 5, 6
 FF_NONE, FF_ROUTED_EXPERTS, FF_DENSE = 0, 1, 2
 NORM_DYT, NORM_LAYER = 0, 1
-FORM_SEQUENTIAL, FORM_PARALLEL = 0, 1
-ACT_XIELU = 1
-ABI_VERSION = 2
+FORM_SEQUENTIAL, FORM_PARALLEL, FORM_STREAMS = 0, 1, 2
+ACT_SILU_GLU, ACT_XIELU, ACT_CLAMPED_GLU = 0, 1, 2
+ROUTER_SIGMOID_INPUT, ROUTER_SOFTMAX_TOP = 0, 1
+ABI_VERSION = 3
 PRECISION_FP32, PRECISION_BF16 = 0, 1
 E_OK, E_INVAL, E_CUDA, E_NOMEM, E_UNSUPPORTED = 0, -1, -2, -3, -5
 
@@ -39,13 +40,17 @@ class Layer(C.Structure):
                 ("act", _i), ("act_p", _f), ("act_q", _f), ("unit_eps", _f), ("n_in", _i), ("k_out", _i), ("w_in", _vp),
                 ("in_bias", _vp), ("w_out", _vp), ("w_pre", _vp), ("rot_freq", _vp), ("talk", _vp), ("head_norm", _vp),
                 ("lower", _vp), ("conv_w", _vp), ("a_log", _vp), ("dt_bias", _vp), ("w_a2", _vp), ("w_g2", _vp),
-                ("rec_state", _vp), ("conv_tail", _vp)]
+                ("rec_state", _vp), ("conv_tail", _vp),
+                # the stream form
+                ("streams", _i), ("hc_in", _vp * 2), ("hc_out", _vp * 2), ("hc_mix", _vp * 2), ("q_rank", _i), ("kv_rank", _i),
+                ("q_lat_norm", _vp), ("kv_lat_norm", _vp), ("w_uq", _vp), ("w_uk_t", _vp), ("w_uv", _vp), ("latent_pages", _vp),
+                ("gate_cap", _f), ("rec_aux", _vp), ("router", _i), ("router_bias", _vp), ("act_limit", _f), ("shared_limit", _f)]
 
 
 class Model(C.Structure):
     _fields_ = [("n_layer", _i), ("width", _i), ("vocab", _i), ("taps", _i), ("page_size", _i), ("max_pages", _i),
                 ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("precision", _i), ("embed", _vp), ("head", _vp),
-                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("logit_scale", _f)]
+                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("logit_scale", _f), ("embed_scale", _f)]
 
 
 _ci = C.c_int

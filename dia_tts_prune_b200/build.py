@@ -17,7 +17,7 @@ LIB = CSRC / "libdia_b200.so"
 SOURCES = ["step_kernel.cu", "aux_kernels.cu", "gemm_tcgen05.cu", "prefill_kernels.cu", "batch_kernel.cu", "engine.cu"]
 HEADERS = ["common.cuh", "engine_internal.h", "sampler.cuh", "gemm_tcgen05.h"]
 LM_LIB = CSRC / "liblm_b200.so"
-LM_SOURCES = ["lm_kernels.cu", "lm_mixers.cu", "lm_engine.cu", "gemm_tcgen05.cu"]          # the tensor-core GEMM is shared with Dia
+LM_SOURCES = ["lm_kernels.cu", "lm_mixers.cu", "lm_streams.cu", "lm_engine.cu", "gemm_tcgen05.cu"]          # the tensor-core GEMM is shared with Dia
 LM_HEADERS = ["lm_internal.h", "lm_device.cuh", "gemm_tcgen05.h", "common.cuh", "engine_internal.h"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]

@@ -46,6 +46,19 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+// activation of a gated unit on its gate g and up u products.  kGluSilu: silu(g) u.  kGluClamped: both are clamped first
+// (g from above, u on both sides), the gate's sigmoid is 1.702 times steeper and the up branch is offset by one:
+// g' sigmoid(1.702 g') (u' + 1)
+constexpr int kGluSilu = 0, kGluClamped = 1;
+__device__ __forceinline__ float glu_act(int kind, float g, float u, float limit) {
+    if (kind == kGluClamped) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * sigmoidf_(1.702f * g) * (u + 1.0f);
+    }
+    return siluf_(g) * u;
+}
+
 // the kernels of a short step are launched with programmatic stream serialization (see pdl_release / pdl_wait)
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

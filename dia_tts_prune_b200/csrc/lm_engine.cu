@@ -28,6 +28,21 @@
 //   out[:, mixer columns:] = act(proj up rows)  xielu_rows
 //   x += out W_out^T                            linear with the residual add (W_out = [W_o | W_down])
 //
+// A record of the stream form (s residual streams with hyper-connection weights, layer norm without bias, a latent
+// attention or a stabilised matrix memory, a clamped gated unit or a mixture of them) runs, per sublayer,
+//   x_j <- sum_s mix[s][j] x_s + out[j] y_prev;  h = layernorm(sum_s in[s] x_s)     streams_step: the previous sublayer's
+//                                               write and this one's read in one launch
+//   proj = h W_in^T                             linear: every projection that reads h
+//   latent attention: latent norms, latent -> pages (latent_prep); q = c_q W_uq^T (linear); q_h -> q_h^T W_uk,h (head_linear);
+//                     attention over the latent pages, all heads on the one latent "key/value head" (talk_attention);
+//                     o_h = W_uv,h (attended latent) * sigmoid(gate) (head_linear)
+//   matrix memory:    log-space gates and running maximum (mlstm_gates); the recurrence with the normaliser as one more
+//                     value column (scalar_gate_scan); read-out / normaliser, head norm, gate (mlstm_finish)
+//   y = out W_o^T                               linear
+//   feed-forward:     [gate | up] product, clamped activation, down product; routed experts grouped as above, their outputs
+//                     weighed by the softmax over the chosen logits inside the next streams_step
+// and after the last layer the streams are summed for the final norm.
+//
 // Products.  With float32 precision every product runs on the fp32 FMA kernels.  With bfloat16 precision a step of at
 // least kTensorRowsMin rows (a prompt portion) runs its products on the tensor cores (the tcgen05 kernel of
 // gemm_tcgen05.cu, bf16 operands, fp32 accumulation in tensor memory): the norm / attention / gate kernels write the
@@ -37,6 +52,7 @@
 // scores, softmax, pages and the residual stream are fp32 in both.
 #include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <cstdint>
 #include <cstdio>
 #include <map>
@@ -98,6 +114,11 @@ struct lm_b200_engine {
     // the parallel layer form: embedding output, [x | x0], stacked projections, recurrence inputs, [mixer out | ff act]
     float *x0, *cat, *proj, *rec, *outcat;
     void *catb, *outcatb;
+    // the stream layer form: the streams [rows][s][width], query latents (bf16 operand), queries carried into the latent
+    // space, attended latents / raw read-outs, normaliser floors, and two constants {0, 1}
+    float *xs, *qlat, *olat, *floorb, *unit;
+    void* cqb;
+    bool stream_form = false;
     float* split_ws;                             // partial results of the key splits of a few rows' attention
     unsigned* split_arrived;                     // ... and their arrival counters (zero between launches)
     // steps of a few rows are captured once per (rows, sequences, wanted) into a CUDA graph over these fixed buffers
@@ -197,8 +218,60 @@ int check_parallel_layer(const lm_b200_model& m, const lm_b200_layer& l) {
     (void)m;
 }
 
+// columns of the stacked projections of a stream record
+struct StreamCols { int q, k, v, ig, fg, gate, lat_q, lat_c, n; };
+StreamCols stream_cols(const lm_b200_layer& l) {
+    StreamCols c{};
+    const int H = l.heads, d = l.dim, dv = l.vdim;
+    int at = 0;
+    if (l.mixer == LM_B200_MIXER_LATENT_ATTENTION) {
+        c.lat_q = at; at += l.q_rank; c.lat_c = at; at += l.kv_rank;
+    } else {
+        c.q = at; at += H * d; c.k = at; at += H * d; c.v = at; at += H * dv; c.ig = at; at += H; c.fg = at; at += H;
+    }
+    c.gate = at; at += H * dv;
+    c.n = (at + 3) & ~3;
+    return c;
+}
+lm::TalkShape latent_shape(const lm_b200_layer& l) {
+    return lm::TalkShape{l.heads, 1, l.kv_rank, l.kv_rank, 0, 1.f, nullptr, nullptr, l.sink};
+}
+
+int check_stream_layer(const lm_b200_model& m, const lm_b200_layer& l) {
+    if (l.streams < 1 || l.streams > 8) return LM_B200_EUNSUPPORTED;
+    if (l.norm_mix_in.kind != LM_B200_NORM_LAYER || !l.norm_mix_in.w) return LM_B200_EINVAL;
+    if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0 || !l.w_in || !l.w_o || l.n_in != stream_cols(l).n) return LM_B200_EINVAL;
+    for (int q = 0; q < (l.ff == LM_B200_FF_NONE ? 1 : 2); ++q)
+        if (!l.hc_in[q] || !l.hc_out[q] || !l.hc_mix[q]) return LM_B200_EINVAL;
+    switch (l.mixer) {
+        case LM_B200_MIXER_LATENT_ATTENTION:
+            if (l.q_rank <= 0 || l.kv_rank <= 0 || !l.q_lat_norm || !l.kv_lat_norm || !l.w_uq || !l.w_uk_t || !l.w_uv ||
+                !l.latent_pages)
+                return LM_B200_EINVAL;
+            if (!lm::talk_attention_supported(latent_shape(l))) return LM_B200_EUNSUPPORTED;
+            break;
+        case LM_B200_MIXER_MLSTM:
+            if (!l.head_norm || !l.rec_state || !l.rec_aux || !(l.gate_cap > 0.f)) return LM_B200_EINVAL;
+            if (l.dim > 256 || l.heads > 256) return LM_B200_EUNSUPPORTED;
+            break;
+        default: return LM_B200_EUNSUPPORTED;
+    }
+    if (l.ff == LM_B200_FF_NONE) return LM_B200_OK;
+    if (!l.norm_ff_in.w || l.norm_ff_in.kind != LM_B200_NORM_LAYER) return LM_B200_EINVAL;
+    if (l.act != LM_B200_ACT_CLAMPED_GLU && l.act != LM_B200_ACT_SILU_GLU) return LM_B200_EUNSUPPORTED;
+    if (l.ff == LM_B200_FF_DENSE) return (l.dense_ff > 0 && l.ws_gate_up && l.ws_down) ? LM_B200_OK : LM_B200_EINVAL;
+    if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EUNSUPPORTED;
+    if (l.experts <= 0 || l.top <= 0 || l.top > l.experts || l.expert_ff <= 0 || l.shared_ff < 0) return LM_B200_EINVAL;
+    if (!l.w_router || !l.w_gate_up || !l.w_down || (l.shared_ff > 0 && (!l.ws_gate_up || !l.ws_down))) return LM_B200_EINVAL;
+    if (l.router != LM_B200_ROUTER_SOFTMAX_TOP) return LM_B200_EUNSUPPORTED;
+    if (3 * (size_t)l.experts * sizeof(int) > 40000) return LM_B200_EUNSUPPORTED;
+    (void)m;
+    return LM_B200_OK;
+}
+
 int check_layer(const lm_b200_model& m, const lm_b200_layer& l) {
     if (l.form == LM_B200_FORM_PARALLEL) return check_parallel_layer(m, l);
+    if (l.form == LM_B200_FORM_STREAMS) return check_stream_layer(m, l);
     if (l.form != LM_B200_FORM_SEQUENTIAL) return LM_B200_EUNSUPPORTED;
     if (l.mixer != LM_B200_MIXER_SINK_ATTENTION) return LM_B200_EUNSUPPORTED;
     if (l.heads <= 0 || l.kv_heads <= 0 || l.heads % l.kv_heads || l.dim <= 0 || l.dim > 256) return LM_B200_EINVAL;
@@ -440,6 +513,122 @@ int parallel_layer(lm_b200_engine* e, const lm_b200_layer& l, const StepView& v,
     return product(e, e->outcat, ob, ko, l.w_out, only == 0 ? e->x : y_out, M, D, ko, only == 0, st);
 }
 
+// ---- the stream form ----------------------------------------------------------------------------------------------------
+// Y = A W^T for an operand that has a contiguous bf16 copy Ab [M][K] (tensor cores) or lives in fp32 rows of stride lda
+int product_ld(lm_b200_engine* e, const float* A, int lda, const void* Ab, const void* W, float* out, int M, int N, int K,
+               cudaStream_t st) {
+    if (Ab && tensor_path(e, M, N, K)) {
+        LCK(dia::launch_gemm_tcgen05_bf16(Ab, 1, W, N, out, M, N, K, kPlain, nullptr, st));
+        return LM_B200_OK;
+    }
+    LCK(lm::launch_linear(A, lda, W, 0, out, N, M, N, K, nullptr, st));
+    return LM_B200_OK;
+}
+
+// y = mixer(h) of a stream record
+int stream_mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, const StepView& v, int M, int n_seq,
+                 float* y, cudaStream_t st) {
+    const int D = e->m.width, H = l.heads, nv = H * l.vdim;
+    const bool bf = e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin;
+    const StreamCols c = stream_cols(l);
+    int rc = product_ld(e, h, D, hb, l.w_in, e->proj, M, c.n, D, st);
+    if (rc) return rc;
+    if (l.mixer == LM_B200_MIXER_LATENT_ATTENTION) {
+        const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
+        const int nq = H * l.dim, nl = H * l.kv_rank;
+        LCK(lm::launch_latent_prep(e->proj, c.n, c.lat_q, l.q_rank, c.lat_c, l.kv_rank, l.q_lat_norm, l.kv_lat_norm, e->m.eps,
+                                   bf ? e->cqb : nullptr, l.latent_pages, pm, v.rm, M, st));
+        rc = product_ld(e, e->proj + c.lat_q, c.n, bf ? e->cqb : nullptr, l.w_uq, e->qk, M, nq, l.q_rank, st);
+        if (rc) return rc;
+        // scores q_h . (W_uk,h c_j) = (W_uk,h^T q_h) . c_j: the query goes into the latent space, with the score multiplier
+        LCK(lm::launch_head_linear(e->qk, nq, l.w_uk_t, e->qlat, nl, nullptr, M, H, l.kv_rank, l.dim, l.scale, nullptr, 0, st));
+        LCK(lm::launch_talk_attention(e->qlat, nl, 0, -1, l.latent_pages, l.latent_pages, pm, latent_shape(l), v.rm, e->olat, nl,
+                                      nullptr, e->split_ws, e->split_arrived, M, st));
+        // sum_j p_j (W_uv,h c_j) = W_uv,h (sum_j p_j c_j), times the sigmoid of the gate columns
+        LCK(lm::launch_head_linear(e->olat, nl, l.w_uv, e->att, nv, bf ? e->attb : nullptr, M, H, l.vdim, l.kv_rank, 1.f,
+                                   e->proj + c.gate, c.n, st));
+    } else {
+        LCK(lm::launch_mlstm_gates(e->proj, c.n, c.ig, c.fg, l.in_bias, l.gate_cap, H, l.rec_aux, v.sm, v.rm, n_seq, e->floorb, st));
+        const lm::ScanInputs si{c.q, c.k, c.fg, c.v, c.ig};      // decay in the forget column, write strength in the input column
+        LCK(lm::launch_scalar_gate_scan(e->proj, c.n, si, H, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq, e->olat,
+                                        H * (l.vdim + 1), st));
+        LCK(lm::launch_mlstm_finish(e->olat, H * (l.vdim + 1), e->floorb, 1.0f / sqrtf((float)l.dim), l.head_norm, e->proj + c.gate,
+                                    c.n, e->m.eps, e->att, bf ? e->attb : nullptr, M, H, l.vdim, st));
+    }
+    return product_ld(e, e->att, nv, bf ? e->attb : nullptr, l.w_o, y, M, D, nv, st);
+}
+
+// one gated unit on all rows: out = act([gate | up] h) W_down^T
+int gated_unit(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, const void* w_gu, const void* w_down,
+               int F, float limit, float* out, cudaStream_t st) {
+    const int D = e->m.width;
+    if (hb && tensor_path(e, M, 2 * F, D) && tensor_path(e, M, D, F)) {
+        LCK(dia::launch_gemm_tcgen05_bf16(hb, 1, w_gu, 2 * F, e->sgu, M, 2 * F, D, kPlain, nullptr, st));
+        LCK(lm::launch_silu_mul(e->sgu, nullptr, e->smidb, M, F, nullptr, st, l.act == LM_B200_ACT_CLAMPED_GLU ? 1 : 0, limit));
+        LCK(dia::launch_gemm_tcgen05_bf16(e->smidb, 1, w_down, D, out, M, D, F, kPlain, nullptr, st));
+        return LM_B200_OK;
+    }
+    if (M <= lm::kRowsKernelMax) {                              // the gate inside the [gate | up] product
+        const lm::GluAct act{l.act == LM_B200_ACT_CLAMPED_GLU ? 1 : 0, limit, limit};
+        LCK(lm::launch_gated_rows(h, D, nullptr, 0, nullptr, 0, F, D, nullptr, w_gu, e->smid, M, F, st, act));
+    } else {
+        LCK(lm::launch_linear(h, D, w_gu, 0, e->sgu, 2 * F, M, 2 * F, D, nullptr, st));
+        LCK(lm::launch_silu_mul(e->sgu, e->smid, nullptr, M, F, nullptr, st, l.act == LM_B200_ACT_CLAMPED_GLU ? 1 : 0, limit));
+    }
+    LCK(lm::launch_linear(e->smid, F, w_down, 0, out, D, M, D, F, nullptr, st));
+    return LM_B200_OK;
+}
+
+// the feed-forward of a stream record: fills what the following streams_step adds (wr->y and, for grouped experts, the
+// expert outputs with their weights)
+int stream_ff(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, lm::StreamWrite* wr,
+              cudaStream_t st) {
+    const int D = e->m.width, E = l.experts, top = l.top, F = l.expert_ff, Sf = l.shared_ff;
+    const int act = l.act == LM_B200_ACT_CLAMPED_GLU ? 1 : 0;
+    wr->y = e->y; wr->parts = nullptr; wr->slot_of = nullptr; wr->sel_w = nullptr; wr->top = 0;
+    if (l.ff == LM_B200_FF_DENSE) return gated_unit(e, l, h, hb, M, l.ws_gate_up, l.ws_down, l.dense_ff, l.act_limit, e->y, st);
+    if (M <= lm::kRowsKernelMax) {
+        const lm::GroupMap rows{e->a_row, e->a_scale, e->a_expert, e->n_slots};
+        LCK(lm::launch_router_rows(h, D, l.w_router, E, top, M, e->z, rows, e->slot_of, st, l.router_bias, true));
+        const lm::GroupMap unscaled{e->a_row, nullptr, e->a_expert, e->n_slots};    // the weight is for the expert's OUTPUT
+        const lm::GluAct ga{act, l.act_limit, l.shared_limit};
+        LCK(lm::launch_gated_rows(h, D, l.w_gate_up, 2LL * F * D, e->mid, M * top, F, D, &unscaled, l.ws_gate_up, e->smid,
+                                  Sf > 0 ? M : 0, Sf, st, ga));
+        LCK(lm::launch_down_combine_rows(e->mid, F, l.w_down, e->a_expert, top, Sf > 0 ? e->smid : nullptr, Sf, l.ws_down, e->y, M, D,
+                                         lm::NormW{nullptr, nullptr, 0.f}, lm::TapOut{}, st, e->a_scale));
+        return LM_B200_OK;
+    }
+    LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, E, M, E, D, nullptr, st));
+    LCK(lm::launch_router_topk(e->z, E, top, M, e->sel_e, e->sel_w, st, l.router_bias, true));
+    const bool tc = hb && tensor_path(e, M, 2 * F, D) && tensor_path(e, M, D, F);
+    const int pad = tc ? dia::kGemmRowTile : lm::kTileRows;
+    const int bound = slots_bound(M, top, E, pad);
+    const lm::GroupMap gm{e->a_row, e->a_scale, e->a_expert, e->n_slots};
+    const lm::GroupMap gather{e->a_row, nullptr, e->a_expert, e->n_slots};
+    LCK(lm::launch_moe_group(e->sel_e, e->sel_w, M * top, top, E, pad, gm, e->slot_of, bound, st));
+    if (tc) {
+        LCK(lm::launch_pack_rows_bf16(h, e->packb, bound, D, &gather, st));
+        const dia::GemmGroups gu_groups{e->a_expert, 2 * F, e->n_slots}, down_groups{e->a_expert, D, e->n_slots};
+        LCK(dia::launch_gemm_tcgen05_bf16(e->packb, 1, l.w_gate_up, (long long)E * 2 * F, e->gu, bound, 2 * F, D, kPlain,
+                                          &gu_groups, st));
+        LCK(lm::launch_silu_mul(e->gu, nullptr, e->midb, bound, F, &gm, st, act, l.act_limit));
+        LCK(dia::launch_gemm_tcgen05_bf16(e->midb, 1, l.w_down, (long long)E * D, e->parts, bound, D, F, kPlain, &down_groups, st));
+    } else {
+        LCK(lm::launch_linear(h, D, l.w_gate_up, 2LL * F * D, e->gu, 2 * F, bound, 2 * F, D, &gather, st));
+        LCK(lm::launch_silu_mul(e->gu, e->mid, nullptr, bound, F, &gm, st, act, l.act_limit));
+        const lm::GroupMap gm_down{nullptr, nullptr, e->a_expert, e->n_slots};
+        LCK(lm::launch_linear(e->mid, F, l.w_down, (long long)D * F, e->parts, D, bound, D, F, &gm_down, st));
+    }
+    wr->y = nullptr;
+    if (Sf > 0) {
+        const int rc = gated_unit(e, l, h, hb, M, l.ws_gate_up, l.ws_down, Sf, l.shared_limit, e->y, st);
+        if (rc) return rc;
+        wr->y = e->y;
+    }
+    wr->parts = e->parts; wr->slot_of = e->slot_of; wr->sel_w = e->sel_w; wr->top = top;
+    return LM_B200_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -453,12 +642,15 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     const lm_b200_model& m = *model;
     if (m.n_layer <= 0 || m.width <= 0 || m.vocab <= 0 || m.taps < 0 || m.taps > lm::kMaxTaps || m.page_size <= 0 ||
         m.max_pages <= 0 || m.n_slots <= 0 || m.max_rows <= 0 ||
-        (m.precision != LM_B200_PRECISION_FP32 && m.precision != LM_B200_PRECISION_BF16) || !m.embed || !m.head || !m.final_norm.w || !m.final_norm.b ||
-        !m.page_table)
+        (m.precision != LM_B200_PRECISION_FP32 && m.precision != LM_B200_PRECISION_BF16) || !m.embed || !m.head || !m.final_norm.w ||
+        (!m.final_norm.b && m.final_norm.kind != LM_B200_NORM_LAYER) || !m.page_table)
         return LM_B200_EINVAL;
     for (int i = 0; i < m.n_layer; ++i) {
         const int rc = check_layer(m, layers[i]);
         if (rc != LM_B200_OK) return rc;
+        // the streams run through the whole stack: a stream record stands among stream records with the same number of them
+        if ((layers[i].form == LM_B200_FORM_STREAMS) != (layers[0].form == LM_B200_FORM_STREAMS)) return LM_B200_EUNSUPPORTED;
+        if (layers[i].form == LM_B200_FORM_STREAMS && layers[i].streams != layers[0].streams) return LM_B200_EINVAL;
     }
     Guard g(device);
     if (!g.ok) return LM_B200_ECUDA;
@@ -470,8 +662,33 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     const size_t R = (size_t)m.max_rows, D = (size_t)m.width;
     size_t qk = 0, att = 0, E = 1, top = 1, F = 1, Sf = 1, slots = 1;
     size_t n_in = 0, k_out = 0, n_rec = 0, split_dim = 0;
+    size_t n_streams = 0, n_lat = 0, q_rank = 0, n_heads = 0;
     bool pre = false;
+    e->stream_form = e->layers[0].form == LM_B200_FORM_STREAMS;
     for (const lm_b200_layer& l : e->layers) {
+        if (l.form == LM_B200_FORM_STREAMS) {
+            n_streams = (size_t)l.streams;
+            n_in = std::max(n_in, (size_t)l.n_in);
+            att = std::max(att, (size_t)l.heads * l.vdim);
+            n_heads = std::max(n_heads, (size_t)l.heads);
+            if (l.mixer == LM_B200_MIXER_LATENT_ATTENTION) {
+                qk = std::max(qk, (size_t)l.heads * l.dim);
+                n_lat = std::max(n_lat, (size_t)l.heads * l.kv_rank);
+                q_rank = std::max(q_rank, (size_t)l.q_rank);
+                split_dim = std::max(split_dim, (size_t)l.heads * (l.kv_rank + 2));
+            } else {
+                n_lat = std::max(n_lat, (size_t)l.heads * (l.vdim + 1));
+            }
+            if (l.ff == LM_B200_FF_DENSE) Sf = std::max(Sf, (size_t)l.dense_ff);
+            if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
+                E = std::max(E, (size_t)l.experts);
+                top = std::max(top, (size_t)l.top);
+                F = std::max(F, (size_t)l.expert_ff);
+                Sf = std::max(Sf, (size_t)l.shared_ff);
+                slots = std::max(slots, (size_t)slots_bound(m.max_rows, l.top, l.experts, dia::kGemmRowTile));
+            }
+            continue;
+        }
         if (l.form == LM_B200_FORM_PARALLEL) {
             n_in = std::max(n_in, (size_t)l.n_in);
             k_out = std::max(k_out, (size_t)l.k_out);
@@ -501,6 +718,8 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
                  o_parts = take(slots * D * 4), o_sgu = take(R * 2 * Sf * 4), o_smid = take(R * Sf * 4), o_hw = take(R * D * 4);
     const size_t o_x0 = take(pre ? R * D * 4 : 0), o_cat = take(pre ? R * 2 * D * 4 : 0), o_proj = take(R * n_in * 4),
                  o_rec = take(R * n_rec * 4), o_outcat = take(R * k_out * 4);
+    const size_t o_xs = take(R * n_streams * D * 4), o_qlat = take(R * n_lat * 4), o_olat = take(R * n_lat * 4),
+                 o_floor = take(R * n_heads * 4), o_unit = take(2 * 4);
     const size_t o_split = take((size_t)lm::kAttnRowsKernelMax * lm::kAttnSplitsMax * split_dim * 4);
     size_t max_heads = 1;
     for (const lm_b200_layer& l : e->layers) max_heads = std::max(max_heads, (size_t)l.heads);
@@ -510,6 +729,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
                  o_midb = take(tcb ? slots * F * 2 : 0), o_smidb = take(tcb ? R * Sf * 2 : 0), o_hwb = take(tcb ? R * D * 2 : 0);
     const size_t o_catb = take(tcb && pre ? R * 2 * D * 2 : 0), o_outcatb = take(tcb ? R * k_out * 2 : 0);
+    const size_t o_cqb = take(tcb ? R * q_rank * 2 : 0);
     if (cudaMalloc(&e->arena, off) != cudaSuccess) {
         (void)cudaGetLastError();
         delete e;
@@ -527,9 +747,13 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->hwb = b + o_hwb;
     e->x0 = (float*)(b + o_x0); e->cat = (float*)(b + o_cat); e->proj = (float*)(b + o_proj); e->rec = (float*)(b + o_rec);
     e->outcat = (float*)(b + o_outcat); e->catb = b + o_catb; e->outcatb = b + o_outcatb;
+    e->xs = (float*)(b + o_xs); e->qlat = (float*)(b + o_qlat); e->olat = (float*)(b + o_olat); e->floorb = (float*)(b + o_floor);
+    e->unit = (float*)(b + o_unit); e->cqb = b + o_cqb;
     e->split_ws = (float*)(b + o_split);
     e->split_arrived = (unsigned*)(b + o_arrived);
-    if (cudaMemset(e->split_arrived, 0, arrived_bytes) != cudaSuccess) {
+    const float unit_host[2] = {0.f, 1.f};
+    if (cudaMemset(e->split_arrived, 0, arrived_bytes) != cudaSuccess ||
+        cudaMemcpy(e->unit, unit_host, sizeof(unit_host), cudaMemcpyHostToDevice) != cudaSuccess) {
         (void)cudaGetLastError();
         cudaFree(e->arena);
         delete e;
@@ -557,11 +781,75 @@ size_t lm_b200_engine_workspace_bytes(const lm_b200_engine* e) { return e ? e->a
 
 namespace {
 
+// the final norm of the wanted rows of e->x and the logits
+int head_rows(lm_b200_engine* e, const StepView& v, int n_want, float* logits_out, cudaStream_t st) {
+    const int D = e->m.width;
+    if (n_want > 0) {
+        // the head is the largest single weight stream: from kHeadTensorRowsMin wanted rows on (a batch of decoding
+        // sequences) the tensor-core kernel reads it once for all rows, where the row kernel reads it once per row
+        const bool tc = e->m.precision == LM_B200_PRECISION_BF16 && n_want >= kHeadTensorRowsMin &&
+                        dia::gemm_tcgen05_shape_ok(n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
+        if (e->m.final_norm.kind == LM_B200_NORM_LAYER)
+            LCK(lm::launch_layernorm_rows(e->x, v.want, e->m.final_norm.w, e->m.final_norm.b, e->m.eps,
+                                          e->m.logit_scale != 0.f ? e->m.logit_scale : 1.f, e->hw, tc ? e->hwb : nullptr, n_want, D, st));
+        else
+            LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
+        if (tc)
+            LCK(dia::launch_gemm_tcgen05_bf16(e->hwb, 1, e->m.head, e->m.vocab, logits_out, n_want, e->m.vocab, D, kPlain, nullptr, st));
+        else
+            LCK(lm::launch_linear(e->hw, D, e->m.head, 0, logits_out, e->m.vocab, n_want, e->m.vocab, D, nullptr, st));
+    }
+    return LM_B200_OK;
+}
+
+
+// every layer of a stream-form model: the streams end up summed in e->x
+int run_stream_layers(lm_b200_engine* e, const StepView& v, int M, int n_seq, float* layers_out, cudaStream_t st) {
+    const int D = e->m.width, s = e->layers[0].streams, n = e->m.n_layer;
+    const float eps = e->m.eps;
+    const bool bf = e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin;
+    void* hb = bf ? e->hb : nullptr;
+    LCK(lm::launch_streams_embed(e->m.embed, v.token, e->m.embed_scale != 0.f ? e->m.embed_scale : 1.f, e->xs, s, M, e->m.vocab, D, st));
+    const lm::StreamWrite none{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0};
+    LCK(lm::launch_streams_step(e->xs, s, none, e->layers[0].hc_in[0], e->layers[0].norm_mix_in.w, eps, nullptr, e->h, hb, M, D, st));
+    for (int i = 0; i < n; ++i) {
+        const lm_b200_layer& l = e->layers[i];
+        int rc = stream_mixer(e, l, e->h, hb, v, M, n_seq, e->y, st);
+        if (rc) return rc;
+        lm::StreamWrite wr{l.hc_mix[0], l.hc_out[0], e->y, nullptr, nullptr, nullptr, 0};
+        if (l.ff != LM_B200_FF_NONE) {
+            LCK(lm::launch_streams_step(e->xs, s, wr, l.hc_in[1], l.norm_ff_in.w, eps, nullptr, e->h, hb, M, D, st));
+            rc = stream_ff(e, l, e->h, hb, M, &wr, st);
+            if (rc) return rc;
+            wr.mix = l.hc_mix[1];
+            wr.out = l.hc_out[1];
+        }
+        // this sublayer's write with the next layer's read, or with the closing sum of the streams
+        if (i + 1 < n) {
+            const lm_b200_layer& nx = e->layers[i + 1];
+            LCK(lm::launch_streams_step(e->xs, s, wr, nx.hc_in[0], nx.norm_mix_in.w, eps, nullptr, e->h, hb, M, D, st));
+            if (layers_out)
+                LCK(lm::launch_streams_step(e->xs, s, none, nullptr, nullptr, eps, nullptr, layers_out + (size_t)i * M * D, nullptr, M, D, st));
+        } else {
+            LCK(lm::launch_streams_step(e->xs, s, wr, nullptr, nullptr, eps, nullptr, e->x, nullptr, M, D, st));
+            if (layers_out && cudaMemcpyAsync(layers_out + (size_t)i * M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, st) !=
+                                  cudaSuccess)
+                return cuda_fail(cudaGetLastError());
+        }
+    }
+    return LM_B200_OK;
+}
+
 // the launch sequence of one step
 int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_want, float* logits_out, float* layers_out,
              cudaStream_t st) {
     const StepView v = view(step, M, n_seq);
     const int D = e->m.width;
+    if (e->stream_form) {
+        const int rc = run_stream_layers(e, v, M, n_seq, layers_out, st);
+        if (rc) return rc;
+        return head_rows(e, v, n_want, logits_out, st);
+    }
     LCK(lm::launch_embed(e->m.embed, v.token, e->x, M, e->m.vocab, D, st));
     bool keep_x0 = false;
     for (const lm_b200_layer& l : e->layers) keep_x0 = keep_x0 || (l.form == LM_B200_FORM_PARALLEL && l.w_pre);
@@ -606,22 +894,7 @@ int run_step(lm_b200_engine* e, const int32_t* step, int M, int n_seq, int n_wan
                 return cuda_fail(cudaGetLastError());
         }
     }
-    if (n_want > 0) {
-        // the head is the largest single weight stream: from kHeadTensorRowsMin wanted rows on (a batch of decoding
-        // sequences) the tensor-core kernel reads it once for all rows, where the row kernel reads it once per row
-        const bool tc = e->m.precision == LM_B200_PRECISION_BF16 && n_want >= kHeadTensorRowsMin &&
-                        dia::gemm_tcgen05_shape_ok(n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
-        if (e->m.final_norm.kind == LM_B200_NORM_LAYER)
-            LCK(lm::launch_layernorm_rows(e->x, v.want, e->m.final_norm.w, e->m.final_norm.b, e->m.eps,
-                                          e->m.logit_scale != 0.f ? e->m.logit_scale : 1.f, e->hw, tc ? e->hwb : nullptr, n_want, D, st));
-        else
-            LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
-        if (tc)
-            LCK(dia::launch_gemm_tcgen05_bf16(e->hwb, 1, e->m.head, e->m.vocab, logits_out, n_want, e->m.vocab, D, kPlain, nullptr, st));
-        else
-            LCK(lm::launch_linear(e->hw, D, e->m.head, 0, logits_out, e->m.vocab, n_want, e->m.vocab, D, nullptr, st));
-    }
-    return LM_B200_OK;
+    return head_rows(e, v, n_want, logits_out, st);
 }
 
 // A step of a few rows is some forty short dependent launches: it is captured once per (rows, sequences, wanted) over
@@ -697,6 +970,14 @@ int lm_b200_op_mixer(lm_b200_engine* e, int layer, const float* h, const int32_t
     if (!g.ok) return LM_B200_ECUDA;
     if (e->layers[layer].form == LM_B200_FORM_PARALLEL)
         return parallel_layer(e, e->layers[layer], view(step, M, n_seq), M, n_seq, 1, h, y, S(stream));
+    if (e->layers[layer].form == LM_B200_FORM_STREAMS) {
+        const void* hb = nullptr;
+        if (e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin) {
+            LCK(lm::launch_pack_rows_bf16(h, e->hb, M, e->m.width, nullptr, S(stream)));
+            hb = e->hb;
+        }
+        return stream_mixer(e, e->layers[layer], h, hb, view(step, M, n_seq), M, n_seq, y, S(stream));
+    }
     return mixer(e, e->layers[layer], h, nullptr, view(step, M, n_seq), M, y, nullptr, lm::TapOut{}, S(stream));
 }
 
@@ -742,6 +1023,25 @@ int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y,
         Guard g(e->device);
         if (!g.ok) return LM_B200_ECUDA;
         return parallel_layer(e, l, StepView{}, M, 0, 2, h, y, S(stream));
+    }
+    if (l.form == LM_B200_FORM_STREAMS) {
+        if (l.ff == LM_B200_FF_NONE) return LM_B200_EINVAL;
+        Guard g(e->device);
+        if (!g.ok) return LM_B200_ECUDA;
+        const void* hb = nullptr;
+        if (e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin) {
+            LCK(lm::launch_pack_rows_bf16(h, e->hb, M, e->m.width, nullptr, S(stream)));
+            hb = e->hb;
+        }
+        lm::StreamWrite wr{};
+        const int rc = stream_ff(e, l, h, hb, M, &wr, S(stream));
+        if (rc) return rc;
+        // y = 0 * y + 1 * (the unit's output + the weighted expert outputs): one stream, mix {0}, out {1}
+        if (cudaMemsetAsync(y, 0, (size_t)M * e->m.width * 4, S(stream)) != cudaSuccess) return cuda_fail(cudaGetLastError());
+        wr.mix = e->unit;
+        wr.out = e->unit + 1;
+        LCK(lm::launch_streams_step(y, 1, wr, nullptr, nullptr, e->m.eps, nullptr, nullptr, nullptr, M, e->m.width, S(stream)));
+        return LM_B200_OK;
     }
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;
     Guard g(e->device);

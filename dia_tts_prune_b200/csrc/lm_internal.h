@@ -33,6 +33,8 @@ struct TapOut {
     float* h;                                         // [M][D]
 };
 struct GroupMap { int* a_row; float* a_scale; int* a_expert; int* n_slots; };   // expert-grouped assignment slots
+// activation of the gated units (kind: kGluSilu / kGluClamped of lm_device.cuh; the clamp of routed / dense and shared units)
+struct GluAct { int kind; float limit; float shared_limit; };
 
 cudaError_t launch_embed(const void* table_bf16, const int* ids, float* out, int M, int V, int D, cudaStream_t st);
 cudaError_t launch_dyt_tapmix(const float* x, const NormW& n, const float* cw, int taps, const float* tail, const RowMeta& rm,
@@ -47,22 +49,25 @@ cudaError_t launch_dyt_tapmix_seq(const float* x, const NormW& n, const float* c
 cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, float* x, int M, int N, int K, const NormW& n,
                                         const TapOut& next, cudaStream_t st);
 cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
-                              int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st);
+                              int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st,
+                              const GluAct& act = GluAct{0, 0.f, 0.f});
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
                                      int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, const TapOut& next,
-                                     cudaStream_t st);
+                                     cudaStream_t st, const float* a_weight = nullptr);
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
-                               int* slot_of, cudaStream_t st);
+                               int* slot_of, cudaStream_t st, const float* bias = nullptr, bool softmax_top = false);
 cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,
                                  float* vcache, const PageMap& pm, int kv_heads, int dim, const RowMeta& rm, int M,
                                  cudaStream_t st);
 cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kcache, const float* vcache, const PageMap& pm,
                                   const AttnShape& a, const RowMeta& rm, float* out, void* out_bf16, float* split_ws,
                                   unsigned* arrived, int M, cudaStream_t st);
-cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st);
+cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st,
+                               const float* bias = nullptr, bool softmax_top = false);
 cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign, int top, int E, int pad, const GroupMap& gm,
                              int* slot_of, int max_slots, cudaStream_t st);
-cudaError_t launch_silu_mul(const float* gu, float* mid, void* mid_bf16, int M, int F, const GroupMap* gm, cudaStream_t st);
+cudaError_t launch_silu_mul(const float* gu, float* mid, void* mid_bf16, int M, int F, const GroupMap* gm, cudaStream_t st,
+                            int act = 0, float limit = 0.f);
 cudaError_t launch_pack_rows_bf16(const float* A, void* Ab, int M, int D, const GroupMap* gm, cudaStream_t st);
 cudaError_t launch_residual_dyt(float* x, const float* y, const float* parts, const int* slot_of, int top, const NormW& n, int M,
                                 int D, cudaStream_t st);
@@ -107,7 +112,41 @@ cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_of
 cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
                                float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
                                cudaStream_t st);
+// the same scan with scalar gates per (row, head): S <- a S + (b k) v^T and one more value column that is the constant 1
+// (the normaliser n <- a n + b k, read out as n . q), so state and read-out have vdim + 1 columns per head.  a and b are
+// columns a_off + h and beta_off + h of the input rows.
+cudaError_t launch_scalar_gate_scan(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
+                                    const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st);
 cudaError_t launch_head_norm_gate(float* o, int ldo, void* o_bf16, const float* w, const float* gate, int ldg, int H, int vdim,
                                   float eps, int M, cudaStream_t st);
+
+// ---- the stream layer form (lm_streams.cu): hyper-connected residual streams, latent attention, stabilised matrix memory ----
+// Per row: [x_j <- sum_s mix[s][j] x_s + out[j] (y + sum_t sel_w[t] parts[slot_of[t]])]  (y == nullptr and parts == nullptr:
+// the streams stay), then u = sum_s in[s] x_s (in == nullptr: the plain sum) and h = layernorm(u) w (w == nullptr: h = u).
+// rows (optional): the gathered rows h is wanted for (then nothing is written to the streams).
+struct StreamWrite { const float* mix; const float* out; const float* y; const float* parts; const int* slot_of;
+                     const float* sel_w; int top; };
+cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, const float* in, const float* norm_w, float eps,
+                                const int* rows, float* h, void* h_bf16, int M, int D, cudaStream_t st);
+cudaError_t launch_streams_embed(const void* table_bf16, const int* ids, float scale, float* X, int streams, int M, int V, int D,
+                                 cudaStream_t st);
+// c_q = rms(proj[:, q_off : q_off + q_rank]) qw in place (+ its bf16 copy), c = rms(proj[:, c_off : c_off + kv_rank]) cw into
+// the latent pages [page][page_size][kv_rank]
+cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* qw,
+                               const float* cw, float eps, void* cq_bf16, float* pages, const PageMap& pm, const RowMeta& rm,
+                               int M, cudaStream_t st);
+// Y[m][h N + n] = alpha * sum_k A[m][h K + k] W[h][n][k]  [* sigmoid(gate[m][h N + n])], fp32 arithmetic on bf16 weights
+cudaError_t launch_head_linear(const float* A, int lda, const void* W, float* Y, int ldy, void* y_bf16, int M, int H, int N, int K,
+                               float alpha, const float* gate, int ldg, cudaStream_t st);
+// log-space gates of the stabilised matrix memory, per (sequence, head) along the sequence's rows: i = cap tanh((z_i + b_i) /
+// cap), f = logsigmoid(cap tanh((z_f + b_f) / cap)), m_t = max(f + m_(t-1), i) (m = 0 before position 0, carried in
+// m_state[slot][head]); the columns i_off + h, f_off + h of the row become a = exp(f + m_(t-1) - m_t), b = exp(i - m_t), and
+// floor_out[row][h] = exp(-m_t)
+cudaError_t launch_mlstm_gates(float* proj, int ld, int i_off, int f_off, const float* bias, float cap, int H, float* m_state,
+                               const SeqMeta& sm, const RowMeta& rm, int n_seq, float* floor_out, cudaStream_t st);
+// o[r][h] = scale * raw[r][h][0:vdim] / (max(|scale * raw[r][h][vdim]|, floor[r][h]) + 1e-6), then / rms over the head, times
+// w[h vdim + c] and sigmoid(gate[r][h vdim + c]); fp32 and the bf16 operand
+cudaError_t launch_mlstm_finish(const float* raw, int ldr, const float* floor_in, float scale, const float* w, const float* gate,
+                                int ldg, float eps, float* out, void* out_bf16, int M, int H, int vdim, cudaStream_t st);
 
 }  // namespace lm

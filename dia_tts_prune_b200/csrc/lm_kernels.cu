@@ -28,9 +28,10 @@
 //                              first tokens, and a value-less sink term in the denominator
 //   sink_attention_tile_kernel the same for prompt portions: 64 queries share the key / value tiles (flash-style)
 //   pack_rows_bf16_kernel      the expert-grouped, score-scaled bf16 operand of the tensor-core products
-//   router_topk_kernel         sigmoid scores and the `top` best experts of every row
+//   router_topk_kernel         the `top` best experts of every row (optional logit bias) with sigmoid scores or the softmax
+//                              over the chosen
 //   moe_group_kernel           groups (row, expert) assignments by expert, padded to the GEMM's row tile
-//   silu_mul_kernel            silu(gate) * up on [gate | up] rows
+//   silu_mul_kernel            the gated unit's activation on [gate | up] rows: silu(gate) * up, or the clamped form
 //   residual_dyt_kernel        x += DynamicTanh(y [+ the row's expert outputs])
 //   dyt_gather_kernel          DynamicTanh of selected rows (the rows whose logits are wanted)
 #include <algorithm>
@@ -349,14 +350,15 @@ linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __
     }
 }
 
-// mid[a][n] = silu(A_a . Wg_e[n]) * (A_a . Wu_e[n]),  W_e = [gate rows (F) | up rows (F)][K].  blockIdx.y < n_assign: the
+// mid[a][n] = act(A_a . Wg_e[n], A_a . Wu_e[n]) (silu(g) u, or the clamped form of glu_act),  W_e = [gate rows (F) | up rows
+// (F)][K].  blockIdx.y < n_assign: the
 // assignment slot a of the routed experts (row, expert and score from the maps); beyond: row blockIdx.y - n_assign through
 // the shared expert Ws (Sf hidden units) into smid.  One grid for both, so that the two weight streams overlap.
 __global__ void __launch_bounds__(256)
 gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, long long w_expert_stride,
                   float* __restrict__ mid, int n_assign, int F, int K, const int* __restrict__ a_row,
                   const float* __restrict__ a_scale, const int* __restrict__ a_expert, const __nv_bfloat16* __restrict__ Ws,
-                  float* __restrict__ smid, int Sf) {
+                  float* __restrict__ smid, int Sf, const GluAct act) {
     pdl_release();
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -384,16 +386,16 @@ gated_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __r
     const float* arow = A + (size_t)src * lda;
     const float g = warp_dot(arow, wg, K, lda, sc, lane, !routed);
     const float u = warp_dot(arow, wg + (size_t)width * K, K, lda, sc, lane);
-    if (lane == 0) *dst = (g / (1.0f + expf(-g))) * u;
+    if (lane == 0) *dst = glu_act(act.kind, g, u, routed ? act.limit : act.shared_limit);
 }
 
-// v = smid[r] . Wsd[n] (with a shared expert) + sum_t mid[r * top + t] . Wd_{e(r, t)}[n];  x[r][n] += DynamicTanh(v), or
-// x[r][n] = v without a norm
+// v = smid[r] . Wsd[n] (with a shared expert) + sum_t [a_weight[r * top + t]] mid[r * top + t] . Wd_{e(r, t)}[n];
+// x[r][n] += DynamicTanh(v), or x[r][n] = v without a norm
 __global__ void __launch_bounds__(256)
 down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat16* __restrict__ Wd, const int* __restrict__ a_expert,
                          int top, const float* __restrict__ smid, int Sf, const __nv_bfloat16* __restrict__ Wsd,
                          float* __restrict__ x, int D, const float* __restrict__ nw, const float* __restrict__ nb, float alpha,
-                         const TapOut next) {
+                         const TapOut next, const float* __restrict__ a_weight) {
     pdl_release();
     const int r = blockIdx.y;
     const int lane = threadIdx.x & 31;
@@ -404,7 +406,8 @@ down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat
     else pdl_wait();
     for (int t = 0; t < top; ++t) {
         const int a = r * top + t;
-        v += warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
+        const float part = warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
+        v = a_weight ? fmaf(a_weight[a], part, v) : v + part;
     }
     if (nw) {
         const float x_new = x[(size_t)r * D + n] + dyt(v, alpha, nw[n], nb[n]);
@@ -416,23 +419,25 @@ down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat
     }
 }
 
-// One CTA per row: router logits z = h . Wr^T (fp32), the `top` largest in descending order (ties: the lower index),
-// scores sigmoid(z), and the assignment maps of the row kernels: slot r * top + t holds (row r, expert, score).
+// One CTA per row: router logits z = h . Wr^T [+ bias] (fp32), the `top` largest in descending order (ties: the lower
+// index), scores sigmoid(z) - or, with softmax_top, the softmax over the chosen logits alone - and the assignment maps of
+// the row kernels: slot r * top + t holds (row r, expert, score).
 __global__ void __launch_bounds__(256)
 router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __restrict__ Wr, int E, int top,
                    float* __restrict__ z_out, int* __restrict__ a_row, float* __restrict__ a_scale, int* __restrict__ a_expert,
-                   int* __restrict__ slot_of, int* __restrict__ n_slots) {
+                   int* __restrict__ slot_of, int* __restrict__ n_slots, const float* __restrict__ bias, int softmax_top) {
     extern __shared__ float zs[];                             // [E]
     pdl_release();
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     if (warp >= E) pdl_wait();                                // (a warp without an expert may still write the maps below)
     for (int e = warp; e < E; e += nwarp) {
-        const float z = warp_dot(h + (size_t)r * D, Wr + (size_t)e * D, D, D, 1.f, lane, e == warp);
+        const float z = warp_dot(h + (size_t)r * D, Wr + (size_t)e * D, D, D, 1.f, lane, e == warp) + (bias ? bias[e] : 0.f);
         if (lane == 0) { zs[e] = z; z_out[(size_t)r * E + e] = z; }
     }
     __syncthreads();
     if (warp != 0) return;
     if (r == 0 && lane == 0) *n_slots = gridDim.x * top;
+    float first = 0.f, den = 0.f;                             // softmax over the chosen: the first is the largest
     for (int t = 0; t < top; ++t) {
         float best = -CUDART_INF_F;
         int bi = 0x7fffffff;
@@ -452,11 +457,16 @@ router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __re
             const int a = r * top + t;
             a_row[a] = r;
             a_expert[a] = bi;
-            a_scale[a] = 1.0f / (1.0f + expf(-best));
+            if (t == 0) first = best;
+            const float sc = softmax_top ? expf(best - first) : 1.0f / (1.0f + expf(-best));
+            den += sc;
+            a_scale[a] = sc;
             slot_of[a] = a;
         }
         __syncwarp();
     }
+    if (softmax_top && lane == 0)
+        for (int t = 0; t < top; ++t) a_scale[r * top + t] /= den;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -897,20 +907,22 @@ sink_attention_tile_kernel(const float* __restrict__ qk, int q_stride, const flo
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// one warp per row: scores s = sigmoid(z); the `top` largest (ties: the lower index) in descending order
+// one warp per row: the `top` largest of z [+ bias] (ties: the lower index) in descending order; scores sigmoid(z), or
+// with softmax_top the softmax over the chosen logits alone
 __global__ void router_topk_kernel(const float* __restrict__ z, int E, int top, int M, int* __restrict__ sel_e,
-                                   float* __restrict__ sel_w) {
+                                   float* __restrict__ sel_w, const float* __restrict__ bias, int softmax_top) {
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (r >= M) return;
     const float* zr = z + (size_t)r * E;
+    float first = 0.f, den = 0.f;
     for (int t = 0; t < top; ++t) {
         float best = -CUDART_INF_F;
         int bi = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
             bool taken = false;
             for (int u = 0; u < t; ++u) taken |= (sel_e[(size_t)r * top + u] == e);
-            const float v = zr[e];
+            const float v = zr[e] + (bias ? bias[e] : 0.f);
             if (!taken && (v > best || (v == best && e < bi))) { best = v; bi = e; }
         }
 #pragma unroll
@@ -921,10 +933,15 @@ __global__ void router_topk_kernel(const float* __restrict__ z, int E, int top, 
         }
         if (lane == 0) {
             sel_e[(size_t)r * top + t] = bi;
-            sel_w[(size_t)r * top + t] = 1.0f / (1.0f + expf(-best));
+            if (t == 0) first = best;
+            const float sc = softmax_top ? expf(best - first) : 1.0f / (1.0f + expf(-best));
+            den += sc;
+            sel_w[(size_t)r * top + t] = sc;
         }
         __syncwarp();
     }
+    if (softmax_top && lane == 0)
+        for (int t = 0; t < top; ++t) sel_w[(size_t)r * top + t] /= den;
 }
 
 // one CTA: counts per expert, group starts padded to `pad` slots, then a_row / a_scale / a_expert per slot and the slot
@@ -965,7 +982,7 @@ __global__ void moe_group_kernel(const int* __restrict__ sel_e, const float* __r
 // ---------------------------------------------------------------------------------------------------------------------
 // mid (fp32) or mid_b (bf16, the operand of a tensor-core product: padding rows are written too, as zeros)
 __global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict__ mid, __nv_bfloat16* __restrict__ mid_b, int F,
-                                const int* __restrict__ a_row, const int* __restrict__ n_slots, int M) {
+                                const int* __restrict__ a_row, const int* __restrict__ n_slots, int M, int act, float limit) {
     const int a = blockIdx.x;
     if (n_slots && a >= min(M, *n_slots)) return;
     const bool pad = a_row && a_row[a] < 0;
@@ -974,7 +991,7 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, float* __restrict_
         float v = 0.f;
         if (!pad) {
             const float g = gu[(size_t)a * 2 * F + c], u = gu[(size_t)a * 2 * F + F + c];
-            v = (g / (1.0f + expf(-g))) * u;
+            v = glu_act(act, g, u, limit);
         }
         if (mid_b) mid_b[(size_t)a * F + c] = __float2bfloat16_rn(v);
         else mid[(size_t)a * F + c] = v;
@@ -1101,26 +1118,27 @@ cudaError_t launch_linear_rows_residual(const float* A, int lda, const void* W, 
 }
 
 cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long w_expert_stride, float* mid, int n_assign, int F,
-                              int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st) {
+                              int K, const GroupMap* gm, const void* Ws, float* smid, int n_shared_rows, int Sf, cudaStream_t st,
+                              const GluAct& act) {
     const int widest = std::max(F, n_shared_rows > 0 ? Sf : 0);
     return launch_pdl(gated_rows_kernel, dim3((widest + 7) / 8, n_assign + n_shared_rows), dim3(256), 0, st, A, lda,
                       reinterpret_cast<const __nv_bfloat16*>(W), w_expert_stride, mid, n_assign, F, K,
                       gm ? (const int*)gm->a_row : nullptr, gm ? (const float*)gm->a_scale : nullptr,
-                      gm ? (const int*)gm->a_expert : nullptr, reinterpret_cast<const __nv_bfloat16*>(Ws), smid, Sf);
+                      gm ? (const int*)gm->a_expert : nullptr, reinterpret_cast<const __nv_bfloat16*>(Ws), smid, Sf, act);
 }
 
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
                                      int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, const TapOut& next,
-                                     cudaStream_t st) {
+                                     cudaStream_t st, const float* a_weight) {
     return launch_pdl(down_combine_rows_kernel, dim3((D + 7) / 8, M), dim3(256), 0, st, mid, F,
                       reinterpret_cast<const __nv_bfloat16*>(Wd), a_expert, top, smid, Sf, reinterpret_cast<const __nv_bfloat16*>(Wsd), x,
-                      D, n.w, n.b, n.alpha, next);
+                      D, n.w, n.b, n.alpha, next, a_weight);
 }
 
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
-                               int* slot_of, cudaStream_t st) {
+                               int* slot_of, cudaStream_t st, const float* bias, bool softmax_top) {
     return launch_pdl(router_rows_kernel, dim3(M), dim3(256), E * sizeof(float), st, h, D, reinterpret_cast<const __nv_bfloat16*>(Wr),
-                      E, top, z, gm.a_row, gm.a_scale, gm.a_expert, slot_of, gm.n_slots);
+                      E, top, z, gm.a_row, gm.a_scale, gm.a_expert, slot_of, gm.n_slots, bias, softmax_top ? 1 : 0);
 }
 
 cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,
@@ -1187,8 +1205,9 @@ cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kc
     return launch_attention_splits<1>(qk, q_stride, kcache, vcache, pm, a, rm, out, ob, M, split_ws, arrived, st);
 }
 
-cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st) {
-    router_topk_kernel<<<(M + 3) / 4, 128, 0, st>>>(z, E, top, M, sel_e, sel_w);
+cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st, const float* bias,
+                               bool softmax_top) {
+    router_topk_kernel<<<(M + 3) / 4, 128, 0, st>>>(z, E, top, M, sel_e, sel_w, bias, softmax_top ? 1 : 0);
     return cudaGetLastError();
 }
 
@@ -1199,9 +1218,10 @@ cudaError_t launch_moe_group(const int* sel_e, const float* sel_w, int n_assign,
     return cudaGetLastError();
 }
 
-cudaError_t launch_silu_mul(const float* gu, float* mid, void* mid_bf16, int M, int F, const GroupMap* gm, cudaStream_t st) {
+cudaError_t launch_silu_mul(const float* gu, float* mid, void* mid_bf16, int M, int F, const GroupMap* gm, cudaStream_t st, int act,
+                            float limit) {
     silu_mul_kernel<<<M, 256, 0, st>>>(gu, mid, reinterpret_cast<__nv_bfloat16*>(mid_bf16), F, gm ? gm->a_row : nullptr,
-                                       gm ? gm->n_slots : nullptr, M);
+                                       gm ? gm->n_slots : nullptr, M, act, limit);
     return cudaGetLastError();
 }
 

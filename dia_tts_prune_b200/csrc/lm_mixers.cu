@@ -21,6 +21,8 @@
 //   gate_prep_kernel          silu(q), the bounded forget gate and biases of the gate-tied recurrence, in place
 //   column_scan_kernel        the recurrence of both recurrent mixers, one value column of one head per 8 lanes:
 //                             S <- a S;  [u = beta (v - S^T k)];  S <- S + w u;  o = S^T q, state carried per sequence
+//   scalar_gate_scan_kernel   the same column layout for a recurrence with one decay and one write strength per token and
+//                             head, and a normaliser carried as one more value column
 //   head_norm_gate_kernel     per-head RMS norm of the read-out (x weight, x gate), fp32 in place and the bf16 operand
 //   xielu_rows_kernel         the dense feed-forward's activation on its slice of the stacked projections
 #include <algorithm>
@@ -55,7 +57,7 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     }
     const float inv = 1.0f / sqrtf(block_sum(v, red) / (float)D + eps);
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const float y = fmaf((xr[c] - mean) * inv, w[c], b[c]) * out_scale;
+        const float y = fmaf((xr[c] - mean) * inv, w[c], b ? b[c] : 0.f) * out_scale;
         out[(size_t)blockIdx.x * D + c] = y;
         if (out_b) out_b[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(y);
     }
@@ -793,6 +795,109 @@ column_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, i
     }
 }
 
+// The same column layout for a recurrence with scalar gates per (token, head):  S[:, c] <- a_t S[:, c] + (b_t k_t) v_t[c],
+// o_t[c] = S[:, c] . q_t.  Column vdim of every head is the normaliser: its value is the constant 1, so it carries
+// n <- a n + b k and reads out n . q.  State and read-out have vdim + 1 columns per head: state[slot][h][c][dim].
+template <int RP>
+__global__ void __launch_bounds__(kScanThreads)
+scalar_gate_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int a_off, int v_off, int b_off, int H, int dim,
+                        int vdim, float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                        const int* __restrict__ seq_count, const int* __restrict__ row_pos, float* __restrict__ o, int ldo) {
+    extern __shared__ float sh[];
+    constexpr int DS = 8 * RP;
+    float* sq = sh;                                           // [TT][DS]
+    float* sk = sq + kScanTT * DS;                            // [TT][DS]
+    float* sv = sk + kScanTT * DS;                            // [TT][16]
+    float* sa = sv + kScanTT * kScanCols;                     // [TT]
+    float* sb = sa + kScanTT;                                 // [TT]
+    pdl_release();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kScanCols, vcols = vdim + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, part = lane & 7, cl = warp * 4 + (lane >> 3);
+    const int col = col0 + cl;
+    const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s], start = row_pos[row0];
+    const bool col_ok = col < vcols;
+    float* st = state + (((size_t)slot * H + h) * vcols + (col_ok ? col : 0)) * dim;
+    float S[RP];
+#pragma unroll
+    for (int r = 0; r < RP; ++r) {
+        const int d = part + 8 * r;
+        S[r] = (start > 0 && col_ok && d < dim) ? st[d] : 0.f;
+    }
+    int src[RP];
+#pragma unroll
+    for (int i = 0; i < RP; ++i) {
+        const int idx = tid + kScanThreads * i, t = idx / DS, d = idx - t * DS;
+        src[i] = d < dim ? t * ld + d : -1;
+    }
+    float rq[RP], rk[RP], rv[2], ra = 0.f, rb = 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = min(kScanTT, n - t0);
+        const float* base = in + (size_t)(row0 + t0) * ld;
+#pragma unroll
+        for (int i = 0; i < RP; ++i) {
+            const bool ok = src[i] >= 0 && (tid + kScanThreads * i) / DS < nt;
+            rq[i] = ok ? base[src[i] + q_off + h * dim] : 0.f;
+            rk[i] = ok ? base[src[i] + k_off + h * dim] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = tid + kScanThreads * i, t = idx / kScanCols, c = col0 + (idx - t * kScanCols);
+            rv[i] = t < nt ? (c < vdim ? base[(size_t)t * ld + v_off + h * vdim + c] : (c == vdim ? 1.f : 0.f)) : 0.f;
+        }
+        if (tid < nt) {
+            ra = base[(size_t)tid * ld + a_off + h];
+            rb = base[(size_t)tid * ld + b_off + h];
+        }
+    };
+    fetch(0);
+    for (int t0 = 0; t0 < n; t0 += kScanTT) {
+        const int nt = min(kScanTT, n - t0);
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < RP; ++i) {
+            const int idx = tid + kScanThreads * i;
+            sq[idx] = rq[i];
+            sk[idx] = rk[i];
+        }
+        sv[tid] = rv[0];
+        sv[tid + kScanThreads] = rv[1];
+        if (tid < kScanTT) { sa[tid] = ra; sb[tid] = rb; }
+        __syncthreads();
+        if (t0 + kScanTT < n) fetch(t0 + kScanTT);
+#pragma unroll 4
+        for (int t = 0; t < nt; ++t) {
+            const float* q = sq + t * DS + part;
+            const float* k = sk + t * DS + part;
+            const float a = sa[t], u = sb[t] * sv[t * kScanCols + cl];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int r = 0; r < RP; r += 4) {
+                S[r] = fmaf(a, S[r], k[8 * r] * u);
+                S[r + 1] = fmaf(a, S[r + 1], k[8 * r + 8] * u);
+                S[r + 2] = fmaf(a, S[r + 2], k[8 * r + 16] * u);
+                S[r + 3] = fmaf(a, S[r + 3], k[8 * r + 24] * u);
+                d0 = fmaf(S[r], q[8 * r], d0);
+                d1 = fmaf(S[r + 1], q[8 * r + 8], d1);
+                d2 = fmaf(S[r + 2], q[8 * r + 16], d2);
+                d3 = fmaf(S[r + 3], q[8 * r + 24], d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if (part == 0 && col_ok) o[(size_t)(row0 + t0 + t) * ldo + h * vcols + col] = dot;
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int r = 0; r < RP; ++r) {
+            const int d = part + 8 * r;
+            if (d < dim) st[d] = S[r];
+        }
+    }
+}
+
 // o[r][h] <- o[r][h] / sqrt(mean(o[r][h]^2) + eps) * w [* gate[r][h]] in place (one warp per row and head), and its bf16 copy
 __global__ void head_norm_gate_kernel(float* __restrict__ o, int ldo, __nv_bfloat16* __restrict__ o_b, const float* __restrict__ w,
                                       const float* __restrict__ gate, int ldg, int H, int vdim, float eps, int M) {
@@ -964,6 +1069,28 @@ cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bo
     if (dim <= 128) SCAN_CASE(16);
     SCAN_CASE(32);
 #undef SCAN_CASE
+}
+
+template <int RP>
+static cudaError_t launch_scalar_scan_inst(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
+                                           const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st) {
+    const size_t smem = (size_t)(2 * kScanTT * 8 * RP + kScanTT * kScanCols + 2 * kScanTT) * 4;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(scalar_gate_scan_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_pdl(scalar_gate_scan_kernel<RP>, dim3(n_seq, H, (vdim + 1 + kScanCols - 1) / kScanCols), dim3(kScanThreads), smem,
+                      st, in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, dim, vdim, state, sm.slot, sm.row0, sm.count,
+                      rm.pos, o, ldo);
+}
+
+cudaError_t launch_scalar_gate_scan(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
+                                    const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st) {
+    if (dim > 256 || H > 65535) return cudaErrorNotSupported;
+    if (dim <= 32) return launch_scalar_scan_inst<4>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
+    if (dim <= 64) return launch_scalar_scan_inst<8>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
+    if (dim <= 128) return launch_scalar_scan_inst<16>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
+    return launch_scalar_scan_inst<32>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
 }
 
 cudaError_t launch_head_norm_gate(float* o, int ldo, void* o_bf16, const float* w, const float* gate, int ldg, int H, int vdim,

@@ -1,0 +1,421 @@
+// lm_streams.cu - kernels of the stream layer form of the language-model path (sm_100a): pre-norm sublayers over several
+// residual streams (hyper-connections), attention over a cached latent, and the gates of a stabilised matrix memory.
+//
+// Same step layout and the same rule as lm_kernels.cu: every kernel computes a row's result from that row and the
+// sequence state it points at, in an order of operations that does not depend on what else is in the batch.  The
+// streams, norms, latents, scores, gates, running maxima and the recurrent state are fp32.
+//
+//   streams_embed_kernel      token rows of a bf16 table times a constant, copied into every stream
+//   streams_step_kernel       the write of one sublayer fused with the read of the next:  x_j <- sum_s mix[s][j] x_s +
+//                             out[j] y (y: the sublayer's output, with the weighted sum of a row's expert outputs added),
+//                             then u = sum_s in[s] x_s and h = layernorm(u) w, fp32 and the bf16 GEMM operand.  Without a
+//                             write it is the first read of a step; without in / w it is the plain sum of the streams
+//   latent_prep_kernel        RMS norms of the query latent (in place, + bf16 operand) and of the key/value latent (into
+//                             the pages: the latent is all an attention layer of this kind caches)
+//   head_linear_*_kernel      per-head products Y[m][h] = alpha A[m][h] . W[h]^T with an optional sigmoid gate: queries
+//                             into the latent space (q_h^T W_uk,h) and attended latents out of it (W_uv,h o_h)
+//   mlstm_gates_kernel        capped log-space input / forget gates and the running maximum m along a sequence's rows ->
+//                             decay exp(f + m' - m), write strength exp(i - m), floor exp(-m) per (row, head)
+//   mlstm_finish_kernel       read-out / (max(|n . q|, floor) + 1e-6), per-head RMS norm, weight, sigmoid gate
+//
+// The attention itself is talk_attention_kernel of lm_mixers.cu with ONE key/value head whose key and value pages are
+// the same latent pages (keys = values = c, head size = latent size), and the recurrence is scalar_gate_scan_kernel.
+#include <algorithm>
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "lm_device.cuh"
+#include "lm_internal.h"
+
+namespace lm {
+
+constexpr int kMaxStreams = 8;
+
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void streams_embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids, float scale,
+                                     float* __restrict__ X, int streams, int V, int D) {
+    pdl_release();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int id = ids[r];
+    const bool ok = id >= 0 && id < V;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const float v = ok ? bf(table[(size_t)id * D + c]) * scale : 0.f;
+        for (int j = 0; j < streams; ++j) X[((size_t)r * streams + j) * D + c] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One CTA per (output) row.  X [M][streams][D].
+__global__ void __launch_bounds__(256)
+streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict__ mix, const float* __restrict__ out,
+                    const float* __restrict__ y, const float* __restrict__ parts, const int* __restrict__ slot_of,
+                    const float* __restrict__ sel_w, int top, const float* __restrict__ in, const float* __restrict__ norm_w,
+                    float eps, const int* __restrict__ rows, float* __restrict__ h, __nv_bfloat16* __restrict__ h_b, int D) {
+    extern __shared__ float u_s[];                            // [D]
+    __shared__ float red[32];
+    __shared__ float mix_s[kMaxStreams * kMaxStreams], out_s[kMaxStreams], in_s[kMaxStreams];
+    pdl_release();
+    const int tid = threadIdx.x, s = streams;
+    const bool write = (mix != nullptr) && !rows;
+    if (tid < s * s) mix_s[tid] = write ? mix[tid] : 0.f;
+    if (tid < s) {
+        out_s[tid] = write ? out[tid] : 0.f;
+        in_s[tid] = in ? in[tid] : 1.f;
+    }
+    pdl_wait();
+    __syncthreads();
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xr = X + (size_t)r * s * D;
+    float sum = 0.f;
+    for (int c = tid; c < D; c += blockDim.x) {
+        float xs[kMaxStreams];
+#pragma unroll
+        for (int j = 0; j < kMaxStreams; ++j) xs[j] = j < s ? xr[(size_t)j * D + c] : 0.f;
+        if (write) {
+            float yv = y ? y[(size_t)r * D + c] : 0.f;
+            if (parts)
+                for (int t = 0; t < top; ++t)
+                    yv = fmaf(sel_w[(size_t)r * top + t], parts[(size_t)slot_of[(size_t)r * top + t] * D + c], yv);
+            float nx[kMaxStreams];
+#pragma unroll
+            for (int j = 0; j < kMaxStreams; ++j) {
+                float v = 0.f;
+                if (j < s) {
+#pragma unroll
+                    for (int i = 0; i < kMaxStreams; ++i)
+                        if (i < s) v = fmaf(mix_s[i * s + j], xs[i], v);
+                    v = fmaf(out_s[j], yv, v);
+                    xr[(size_t)j * D + c] = v;
+                }
+                nx[j] = v;
+            }
+#pragma unroll
+            for (int j = 0; j < kMaxStreams; ++j) xs[j] = nx[j];
+        }
+        float uv = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxStreams; ++j)
+            if (j < s) uv = fmaf(in_s[j], xs[j], uv);
+        if (h) {
+            u_s[c] = uv;
+            sum += uv;
+        }
+    }
+    if (!h) return;
+    if (!norm_w) {                                            // the plain read
+        __syncthreads();
+        for (int c = tid; c < D; c += blockDim.x) {
+            h[(size_t)blockIdx.x * D + c] = u_s[c];
+            if (h_b) h_b[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(u_s[c]);
+        }
+        return;
+    }
+    const float mean = block_sum(sum, red) / (float)D;
+    float v = 0.f;
+    for (int c = tid; c < D; c += blockDim.x) {
+        const float d = u_s[c] - mean;
+        v = fmaf(d, d, v);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(v, red) / (float)D + eps);
+    for (int c = tid; c < D; c += blockDim.x) {
+        const float o = (u_s[c] - mean) * inv * norm_w[c];
+        h[(size_t)blockIdx.x * D + c] = o;
+        if (h_b) h_b[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(o);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One CTA per row.  pages: [page][page_size][kv_rank].
+__global__ void __launch_bounds__(256)
+latent_prep_kernel(float* __restrict__ proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* __restrict__ qw,
+                   const float* __restrict__ cw, float eps, __nv_bfloat16* __restrict__ cq_b, float* __restrict__ pages,
+                   const int* __restrict__ table, int max_pages, int page_size, const int* __restrict__ row_slot,
+                   const int* __restrict__ row_pos) {
+    __shared__ float red[32];
+    pdl_release();
+    pdl_wait();
+    const int r = blockIdx.x, tid = threadIdx.x;
+    float* row = proj + (size_t)r * ld;
+    float ss = 0.f;
+    for (int c = tid; c < q_rank; c += blockDim.x) ss = fmaf(row[q_off + c], row[q_off + c], ss);
+    const float qinv = 1.0f / sqrtf(block_sum(ss, red) / (float)q_rank + eps);
+    for (int c = tid; c < q_rank; c += blockDim.x) {
+        const float v = row[q_off + c] * qinv * qw[c];
+        row[q_off + c] = v;
+        if (cq_b) cq_b[(size_t)r * q_rank + c] = __float2bfloat16_rn(v);
+    }
+    ss = 0.f;
+    for (int c = tid; c < kv_rank; c += blockDim.x) ss = fmaf(row[c_off + c], row[c_off + c], ss);
+    const float cinv = 1.0f / sqrtf(block_sum(ss, red) / (float)kv_rank + eps);
+    const int pos = row_pos[r];
+    const int page = table[(size_t)row_slot[r] * max_pages + pos / page_size];
+    float* dst = pages + ((size_t)page * page_size + pos % page_size) * kv_rank;
+    for (int c = tid; c < kv_rank; c += blockDim.x) dst[c] = row[c_off + c] * cinv * cw[c];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Y[m][h N + n] = alpha * sum_k A[m][h K + k] W[h][n][k]  [* sigmoid(gate[m][h N + n])].  64 x 64 x 16 tiles of fp32 FMAs,
+// blockIdx.z = head.
+constexpr int HB = 64, HK = 16;
+
+__global__ void __launch_bounds__(256)
+head_linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, float* __restrict__ Y, int ldy,
+                        __nv_bfloat16* __restrict__ Yb, int M, int N, int K, float alpha, const float* __restrict__ gate, int ldg) {
+    __shared__ __align__(16) float As[HK][HB + 4];
+    __shared__ __align__(16) float Bs[HK][HB + 4];
+    const int hd = blockIdx.z, m0 = blockIdx.y * HB, n0 = blockIdx.x * HB;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    const float* arow = (m0 + lr < M) ? A + (size_t)(m0 + lr) * lda + (size_t)hd * K : nullptr;
+    const __nv_bfloat16* wrow = (n0 + lr < N) ? W + ((size_t)hd * N + n0 + lr) * K : nullptr;
+    const bool a_vec = (lda % 4 == 0) && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    const bool w_vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 7) == 0);
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HK) {
+        float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f};
+        const int k = k0 + lk;
+        if (arow) {
+            if (a_vec && k + 3 < K) {
+                const float4 v = *reinterpret_cast<const float4*>(arow + k);
+                a4[0] = v.x; a4[1] = v.y; a4[2] = v.z; a4[3] = v.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k + i < K) a4[i] = arow[k + i];
+            }
+        }
+        if (wrow) {
+            if (w_vec && k + 3 < K) {
+                const uint2 v = *reinterpret_cast<const uint2*>(wrow + k);
+                const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+                const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+                b4[0] = __low2float(p0); b4[1] = __high2float(p0); b4[2] = __low2float(p1); b4[3] = __high2float(p1);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) if (k + i < K) b4[i] = bf(wrow[k + i]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            As[lk + i][lr] = a4[i];
+            Bs[lk + i][lr] = b4[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HK; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+            const float4 bv = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+            const float a[4] = {av.x, av.y, av.z, av.w}, b[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j] * alpha;
+            if (gate) v *= sigmoidf_(gate[(size_t)m * ldg + (size_t)hd * N + n]);
+            Y[(size_t)m * ldy + (size_t)hd * N + n] = v;
+            if (Yb) Yb[(size_t)m * ldy + (size_t)hd * N + n] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+// the same for a handful of rows: one warp per output element, the weights stream once per row
+__global__ void __launch_bounds__(256)
+head_linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, float* __restrict__ Y, int ldy,
+                        __nv_bfloat16* __restrict__ Yb, int H, int N, int K, float alpha, const float* __restrict__ gate, int ldg) {
+    pdl_release();
+    const int m = blockIdx.y, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (col >= H * N) return;
+    const int hd = col / N;
+    const __nv_bfloat16* wrow = W + (size_t)col * K;          // W[h][n][k] is row h N + n of a [H N][K] matrix
+    const bool vec = (K % 4 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 7) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    uint2 w0 = make_uint2(0u, 0u);
+    if (vec && lane * 4 < K) w0 = *reinterpret_cast<const uint2*>(wrow + lane * 4);
+    pdl_wait();
+    const float* arow = A + (size_t)m * lda + (size_t)hd * K;
+    float acc = 0.f;
+    if (vec) {
+        for (int k = lane * 4; k < K; k += 128) {
+            const uint2 wv = k == lane * 4 ? w0 : *reinterpret_cast<const uint2*>(wrow + k);
+            const float4 x = *reinterpret_cast<const float4*>(arow + k);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            acc = fmaf(x.x, __low2float(p[0]), acc);
+            acc = fmaf(x.y, __high2float(p[0]), acc);
+            acc = fmaf(x.z, __low2float(p[1]), acc);
+            acc = fmaf(x.w, __high2float(p[1]), acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(arow[k], bf(wrow[k]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+        float v = acc * alpha;
+        if (gate) v *= sigmoidf_(gate[(size_t)m * ldg + col]);
+        Y[(size_t)m * ldy + col] = v;
+        if (Yb) Yb[(size_t)m * ldy + col] = __float2bfloat16_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// One CTA per scheduled sequence.  The sequence's rows go through shared memory in chunks: all threads turn the raw gate
+// columns into log-space gates, one thread per head walks the chunk in order (the running maximum is the only thing that
+// passes from row to row), all threads write decay, write strength and floor back.
+constexpr int kGateChunk = 2048;                              // (row, head) pairs per chunk
+
+__device__ __forceinline__ float logsigmoidf_(float z) { return z < -20.f ? z : -log1pf(expf(-z)); }
+
+__global__ void __launch_bounds__(256)
+mlstm_gates_kernel(float* __restrict__ proj, int ld, int i_off, int f_off, const float* __restrict__ bias, float cap, int H,
+                   float* __restrict__ m_state, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                   const int* __restrict__ seq_count, const int* __restrict__ row_pos, float* __restrict__ floor_out) {
+    __shared__ float gi[kGateChunk], gf[kGateChunk], ge[kGateChunk];
+    pdl_release();
+    pdl_wait();
+    const int s = blockIdx.x, tid = threadIdx.x;              // H <= blockDim.x: thread h walks head h
+    const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s], start = row_pos[row0];
+    const int rows_per = kGateChunk / H;
+    float m = 0.f;                                            // the running maximum starts at 0 with the sequence
+    if (tid < H && start > 0) m = m_state[(size_t)slot * H + tid];
+    for (int t0 = 0; t0 < n; t0 += rows_per) {
+        const int nt = min(rows_per, n - t0);
+        __syncthreads();
+        for (int idx = tid; idx < nt * H; idx += blockDim.x) {
+            const int t = idx / H, h = idx - t * H;
+            const float* row = proj + (size_t)(row0 + t0 + t) * ld;
+            const float zi = row[i_off + h] + (bias ? bias[i_off + h] : 0.f);
+            const float zf = row[f_off + h] + (bias ? bias[f_off + h] : 0.f);
+            gi[idx] = cap * tanhf(zi / cap);
+            gf[idx] = logsigmoidf_(cap * tanhf(zf / cap));
+        }
+        __syncthreads();
+        if (tid < H) {
+            for (int t = 0; t < nt; ++t) {
+                const int idx = t * H + tid;
+                const float i = gi[idx], f = gf[idx];
+                const float mn = fmaxf(f + m, i);
+                gi[idx] = expf(i - mn);                       // write strength
+                gf[idx] = expf(f + m - mn);                   // decay
+                ge[idx] = expf(-mn);                          // floor of the normaliser
+                m = mn;
+            }
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nt * H; idx += blockDim.x) {
+            const int t = idx / H, h = idx - t * H;
+            float* row = proj + (size_t)(row0 + t0 + t) * ld;
+            row[i_off + h] = gi[idx];
+            row[f_off + h] = gf[idx];
+            floor_out[(size_t)(row0 + t0 + t) * H + h] = ge[idx];
+        }
+    }
+    if (tid < H) m_state[(size_t)slot * H + tid] = m;
+}
+
+// one warp per (row, head).  raw [M][H][vdim + 1]: the read-out and, in its last column, n . q
+__global__ void __launch_bounds__(256)
+mlstm_finish_kernel(const float* __restrict__ raw, int ldr, const float* __restrict__ floor_in, float scale,
+                    const float* __restrict__ w, const float* __restrict__ gate, int ldg, float eps, float* __restrict__ out,
+                    __nv_bfloat16* __restrict__ out_b, int M, int H, int vdim) {
+    pdl_release();
+    pdl_wait();
+    const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (idx >= M * H) return;
+    const int r = idx / H, h = idx - r * H;
+    const float* src = raw + (size_t)r * ldr + (size_t)h * (vdim + 1);
+    const float den = fmaxf(fabsf(src[vdim] * scale), floor_in[(size_t)r * H + h]) + 1e-6f;
+    const float mult = scale / den;
+    float ss = 0.f;
+    for (int c = lane; c < vdim; c += 32) {
+        const float v = src[c] * mult;
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    const size_t base = (size_t)r * H * vdim + (size_t)h * vdim;
+    for (int c = lane; c < vdim; c += 32) {
+        float y = src[c] * mult * inv * w[(size_t)h * vdim + c];
+        if (gate) y *= sigmoidf_(gate[(size_t)r * ldg + (size_t)h * vdim + c]);
+        out[base + c] = y;
+        if (out_b) out_b[base + c] = __float2bfloat16_rn(y);
+    }
+}
+
+// ---- launchers --------------------------------------------------------------------------------------------------------
+cudaError_t launch_streams_embed(const void* table, const int* ids, float scale, float* X, int streams, int M, int V, int D,
+                                 cudaStream_t st) {
+    return launch_pdl(streams_embed_kernel, dim3(M), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(table), ids, scale, X,
+                      streams, V, D);
+}
+
+cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, const float* in, const float* norm_w, float eps,
+                                const int* rows, float* h, void* h_bf16, int M, int D, cudaStream_t st) {
+    if (streams < 1 || streams > kMaxStreams) return cudaErrorNotSupported;
+    const size_t smem = (size_t)D * 4;
+    static size_t allowed[64] = {};
+    if (smem > 48 * 1024) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64 || allowed[dev] < smem) {
+            e = cudaFuncSetAttribute(streams_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) allowed[dev] = smem;
+        }
+    }
+    return launch_pdl(streams_step_kernel, dim3(M), dim3(256), smem, st, X, streams, wr.mix, wr.out, wr.y, wr.parts, wr.slot_of,
+                      wr.sel_w, wr.top, in, norm_w, eps, rows, h, reinterpret_cast<__nv_bfloat16*>(h_bf16), D);
+}
+
+cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* qw,
+                               const float* cw, float eps, void* cq_bf16, float* pages, const PageMap& pm, const RowMeta& rm,
+                               int M, cudaStream_t st) {
+    return launch_pdl(latent_prep_kernel, dim3(M), dim3(256), 0, st, proj, ld, q_off, q_rank, c_off, kv_rank, qw, cw, eps,
+                      reinterpret_cast<__nv_bfloat16*>(cq_bf16), pages, pm.table, pm.max_pages, pm.page_size, rm.slot, rm.pos);
+}
+
+cudaError_t launch_head_linear(const float* A, int lda, const void* W, float* Y, int ldy, void* y_bf16, int M, int H, int N, int K,
+                               float alpha, const float* gate, int ldg, cudaStream_t st) {
+    const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
+    __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y_bf16);
+    if (M <= kRowsKernelMax)
+        return launch_pdl(head_linear_rows_kernel, dim3((H * N + 7) / 8, M), dim3(256), 0, st, A, lda, w, Y, ldy, yb, H, N, K, alpha,
+                          gate, ldg);
+    if (H > 65535) return cudaErrorNotSupported;
+    head_linear_tile_kernel<<<dim3((N + HB - 1) / HB, (M + HB - 1) / HB, H), 256, 0, st>>>(A, lda, w, Y, ldy, yb, M, N, K, alpha, gate,
+                                                                                          ldg);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mlstm_gates(float* proj, int ld, int i_off, int f_off, const float* bias, float cap, int H, float* m_state,
+                               const SeqMeta& sm, const RowMeta& rm, int n_seq, float* floor_out, cudaStream_t st) {
+    if (H > 256) return cudaErrorNotSupported;                // one thread per head walks the running maximum
+    return launch_pdl(mlstm_gates_kernel, dim3(n_seq), dim3(256), 0, st, proj, ld, i_off, f_off, bias, cap, H, m_state, sm.slot,
+                      sm.row0, sm.count, rm.pos, floor_out);
+}
+
+cudaError_t launch_mlstm_finish(const float* raw, int ldr, const float* floor_in, float scale, const float* w, const float* gate,
+                                int ldg, float eps, float* out, void* out_bf16, int M, int H, int vdim, cudaStream_t st) {
+    return launch_pdl(mlstm_finish_kernel, dim3((M * H + 7) / 8), dim3(256), 0, st, raw, ldr, floor_in, scale, w, gate, ldg, eps,
+                      out, reinterpret_cast<__nv_bfloat16*>(out_bf16), M, H, vdim);
+}
+
+}  // namespace lm

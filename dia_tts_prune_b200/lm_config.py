@@ -1,4 +1,5 @@
-"""Configuration schemas of the decoder-only language models (``config.json`` of a model folder): Pubopel and Kupelix.
+"""Configuration schemas of the decoder-only language models (``config.json`` of a model folder): Pubopel, Kupelix and
+Luketar.
 
 Every size and every per-model constant comes from the file.  Optional entries that are absent switch their
 mechanism off: no ``mask`` is full causal attention, no ``softcap`` leaves scores uncapped, ``mlp: null`` is a layer
@@ -188,7 +189,98 @@ class KupelixConfig(BaseModel, frozen=True):
         return out + [(i, False) for i in range(b, n)]
 
 
-CONFIGS = {"pubopel": PubopelConfig, "kupelix": KupelixConfig}
+# ---- Luketar: pre-norm sublayers over hyper-connected residual streams, latent attention / mLSTM mixers, clamped gated units ----
+class LatentAttentionMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    dim: int = Field(gt=0)                       # query / key size per head
+    vdim: int = Field(gt=0)
+    q_rank: int = Field(gt=0)                    # size of the query latent
+    kv_rank: int = Field(gt=0)                   # size of the cached key/value latent
+    scale: float
+
+
+class MlstmMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    dim: int = Field(gt=0)
+    vdim: int = Field(gt=0)
+    gate_cap: float = Field(gt=0.0)              # gate pre-activations z become cap tanh(z / cap)
+
+
+class GatedUnitConfig(BaseModel, frozen=True):
+    ff: int = Field(gt=0)
+    limit: float = Field(gt=0.0)                 # clamp of the gate (from above) and of the up branch (both sides)
+
+
+class GatedDenseMlpConfig(BaseModel, frozen=True):
+    kind: Literal["dense"]
+    ff: int = Field(gt=0)
+    limit: float = Field(gt=0.0)
+
+
+class GatedMoeMlpConfig(BaseModel, frozen=True):
+    kind: Literal["moe"]
+    expert: GatedUnitConfig
+    router: RouterConfig
+    shared: Optional[GatedUnitConfig] = None
+
+
+GatedMlp = Annotated[Union[GatedDenseMlpConfig, GatedMoeMlpConfig], Field(discriminator="kind")]
+
+
+class LuketarAttentionLayer(BaseModel, frozen=True):
+    type: Literal["latent_attention"]
+    mixer: LatentAttentionMixerConfig
+    mlp: Optional[GatedMlp] = None
+    weights_of: Optional[int] = Field(default=None, ge=0)   # this layer runs with that layer's weights and a state of its own
+
+
+class LuketarMlstmLayer(BaseModel, frozen=True):
+    type: Literal["mlstm"]
+    mixer: MlstmMixerConfig
+    mlp: Optional[GatedMlp] = None
+    weights_of: Optional[int] = Field(default=None, ge=0)
+
+
+LuketarLayer = Annotated[Union[LuketarAttentionLayer, LuketarMlstmLayer], Field(discriminator="type")]
+
+
+class EmbeddingConfig(BaseModel, frozen=True):
+    scale: float = 1.0
+
+
+class LuketarConfig(BaseModel, frozen=True):
+    architecture: Literal["Luketar"] = "Luketar"
+    vocab: int = Field(gt=0)
+    width: int = Field(gt=0)
+    layers: list[LuketarLayer] = Field(min_length=1)
+    norm: NormConfig
+    embedding: EmbeddingConfig = EmbeddingConfig()
+    streams: Optional[int] = Field(default=None, ge=1, le=8)    # residual streams with hyper-connections; None: one plain residual
+
+    @classmethod
+    def load(cls, path: str | Path) -> "LuketarConfig":
+        return cls.model_validate(json.loads(Path(path).read_text(encoding="utf-8")))
+
+    def weight_layer(self, i: int) -> int:
+        """The layer whose tensors layer ``i`` uses."""
+        j = self.layers[i].weights_of
+        return i if j is None else j
+
+    def check(self) -> None:
+        for i, layer in enumerate(self.layers):
+            j = layer.weights_of
+            if j is not None:
+                if j >= len(self.layers) or j == i or self.layers[j].weights_of is not None:
+                    raise ValueError(f"layer {i}: weights_of ({j}) must name another layer that has weights of its own")
+                other = self.layers[j]
+                if (other.type, other.mixer, other.mlp) != (layer.type, layer.mixer, layer.mlp):
+                    raise ValueError(f"layer {i}: its entry differs from layer {j}, whose weights it uses")
+            f = layer.mlp
+            if f is not None and f.kind == "moe" and f.router.top > f.router.experts:
+                raise ValueError(f"layer {i}: top ({f.router.top}) exceeds experts ({f.router.experts})")
+
+
+CONFIGS = {"pubopel": PubopelConfig, "kupelix": KupelixConfig, "luketar": LuketarConfig}
 
 
 def load_config(raw: dict):

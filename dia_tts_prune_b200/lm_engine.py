@@ -28,7 +28,7 @@ def launch_count() -> int:
 class LMEngine:
     def __init__(self, layers: list, embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh | LayerNorm, *,
                  width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024,
-                 precision: str = "bfloat16", step_graphs: bool = True, logit_scale: float = 1.0):
+                 precision: str = "bfloat16", step_graphs: bool = True, logit_scale: float = 1.0, embed_scale: float = 1.0):
         """``layers``: the layer records in execution order (a layer that runs twice per token appears twice, each time
         with the state record of its own index)."""
         if not torch.cuda.is_available():
@@ -57,6 +57,7 @@ class LMEngine:
         m.page_table = state.page_table.data_ptr()
         m.step_graphs = 1 if step_graphs else 0
         m.logit_scale = float(logit_scale)
+        m.embed_scale = float(embed_scale)
         recs = (_lm_lib.Layer * len(layers))()
         for i, layer in enumerate(layers):
             layer.fill(recs[i], state.record_state(i))

@@ -15,11 +15,20 @@ Beside ``layers.py`` (Dia's RMSNorm / rotary attention / gated MLP modules) this
   * :class:`Hgrn2` - gated linear recurrence whose forget gate (with a learned lower bound) also sets the write strength;
   * :class:`ChannelDelta` - gated delta rule with a decay per head and key channel, short causal convolutions on q, k, v,
     unit-vector q and k, and a low-rank sigmoid output gate;
-  * :class:`DenseXielu` - up projection, xIELU activation, down projection.
+  * :class:`DenseXielu` - up projection, xIELU activation, down projection;
+  * :class:`HyperConnection` - read, mix and write weights of one sublayer over several residual streams;
+  * :class:`LatentAttention` - softmax attention whose keys and values are up-projections of ONE cached normed latent per
+    token (the queries go through a normed latent of their own), with a value-less sink logit and an elementwise sigmoid
+    output gate;
+  * :class:`MLstm` - matrix memory with an exponential input gate, capped gate pre-activations, a running maximum that
+    keeps the exponentials in range and a normaliser state;
+  * :class:`GatedUnit` - gate / up / down unit with the clamped activation ``g' sigmoid(1.702 g') (u' + 1)``; the same
+    activation, a logit bias and softmax-over-the-chosen output weights are options of :class:`RoutedExperts`.
 All constants are constructor arguments; a design picks and combines them per layer (:class:`MixLayer` runs its
-sublayers one after the other, :class:`ParallelLayer` feeds one norm to mixer and feed-forward and adds both).  The
-arithmetic lives in ``csrc/lm_kernels.cu`` and ``csrc/lm_mixers.cu``; these classes only keep device tensors alive and
-fill ``lm_b200_layer``.
+sublayers one after the other, :class:`ParallelLayer` feeds one norm to mixer and feed-forward and adds both,
+:class:`StreamLayer` runs pre-norm sublayers over hyper-connected streams).  The arithmetic lives in
+``csrc/lm_kernels.cu``, ``csrc/lm_mixers.cu`` and ``csrc/lm_streams.cu``; these classes only keep device tensors alive
+and fill ``lm_b200_layer``.
 """
 
 from __future__ import annotations
@@ -72,8 +81,15 @@ class SinkAttention:
 
 
 class RoutedExperts:
-    def __init__(self, router, gates: list, ups: list, downs: list, *, top: int, shared=None, device=None):
-        """``gates[e] / ups[e]: [ff, width]``, ``downs[e]: [width, ff]``; ``shared``: (gate, up, down) or None."""
+    def __init__(self, router, gates: list, ups: list, downs: list, *, top: int, shared=None, device=None,
+                 router_bias=None, softmax_top: bool = False, limit: float | None = None, shared_limit: float | None = None):
+        """``gates[e] / ups[e]: [ff, width]``, ``downs[e]: [width, ff]``; ``shared``: (gate, up, down) or None.
+        ``softmax_top``: the softmax over the chosen logits weighs the experts' OUTPUTS (otherwise sigmoid scores scale
+        their inputs); ``limit`` / ``shared_limit``: the clamped activation instead of silu(g) u."""
+        self.router_bias = None if router_bias is None else _f32(router_bias, device)
+        self.softmax_top = bool(softmax_top)
+        self.limit = None if limit is None else float(limit)
+        self.shared_limit = float(shared_limit) if shared_limit is not None else self.limit
         self.experts, self.top, self.ff = len(gates), int(top), int(gates[0].shape[0])
         self.w_router = _bf16(router, device)
         self.w_gate_up = _bf16(torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]), device)
@@ -130,12 +146,12 @@ class MixLayer:
 
 # ---- the parallel form ------------------------------------------------------------------------------------------------
 class LayerNorm:
-    def __init__(self, weight: torch.Tensor, bias: torch.Tensor, device):
-        self.w, self.b = _f32(weight, device), _f32(bias, device)
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, device):
+        self.w, self.b = _f32(weight, device), None if bias is None else _f32(bias, device)
 
     def fill(self, rec) -> None:
         from ._lm_lib import NORM_LAYER
-        rec.w, rec.b, rec.alpha, rec.kind = self.w.data_ptr(), self.b.data_ptr(), 0.0, NORM_LAYER
+        rec.w, rec.b, rec.alpha, rec.kind = self.w.data_ptr(), self.b.data_ptr() if self.b is not None else None, 0.0, NORM_LAYER
 
 
 def rotary_angles(base: float, dims: int, scaling=None) -> torch.Tensor:
@@ -331,3 +347,146 @@ class LayerRun:
     def fill(self, rec, st) -> None:
         self.layer.fill(rec, st)
         rec.w_pre = self.pre.data_ptr() if self.pre is not None else None
+
+
+# ---- the stream form ----------------------------------------------------------------------------------------------------
+class HyperConnection:
+    """One sublayer's weights over ``s`` residual streams: it reads ``u = sum_s w_in[s] x_s`` and writes
+    ``x_j <- sum_s w_mix[s, j] x_s + w_out[j] y``.  :meth:`residual` is the plain residual sum as one stream."""
+
+    def __init__(self, w_in, w_out, w_mix, device):
+        self.streams = int(w_in.numel())
+        if tuple(w_out.shape) != (self.streams,) or tuple(w_mix.shape) != (self.streams, self.streams):
+            raise ValueError("hyper-connection weights do not match the number of streams")
+        self.w_in, self.w_out, self.w_mix = _f32(w_in, device), _f32(w_out, device), _f32(w_mix, device)
+
+    @classmethod
+    def residual(cls, device) -> "HyperConnection":
+        return cls(torch.ones(1), torch.ones(1), torch.ones((1, 1)), device)
+
+
+class LatentAttention:
+    kind = "latent_attention"
+
+    def __init__(self, w_dq, q_lat_norm, w_uq, w_dkv, kv_lat_norm, w_uk, w_uv, w_gate, w_o, *, heads: int, dim: int, vdim: int,
+                 scale: float, sink=None, device=None):
+        self.heads, self.dim, self.vdim, self.scale = int(heads), int(dim), int(vdim), float(scale)
+        self.q_rank, self.kv_rank = int(w_dq.shape[0]), int(w_dkv.shape[0])
+        if (tuple(w_uq.shape) != (heads * dim, self.q_rank) or tuple(w_uk.shape) != (heads * dim, self.kv_rank)
+                or tuple(w_uv.shape) != (heads * vdim, self.kv_rank) or tuple(w_gate.shape)[0] != heads * vdim):
+            raise ValueError("projection shapes do not match heads x dim and the latent sizes")
+        self.in_rows, self.in_bias, self.w_o = [w_dq, w_dkv, w_gate], None, w_o
+        self.q_lat_norm, self.kv_lat_norm = _f32(q_lat_norm, device), _f32(kv_lat_norm, device)
+        self.w_uq = _bf16(w_uq, device)
+        # scores are taken in the latent space: q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, so the kernels want W_uk,h^T
+        self.w_uk_t = _bf16(w_uk.reshape(heads, dim, self.kv_rank).transpose(1, 2), device)
+        self.w_uv = _bf16(w_uv, device)                           # [heads][vdim][kv_rank] as stored
+        self.sink = None if sink is None else _f32(sink, device)
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec(latent=self.kv_rank)
+
+    def fill(self, rec, st) -> None:
+        from ._lm_lib import MIXER_LATENT_ATTENTION
+        rec.mixer = MIXER_LATENT_ATTENTION
+        rec.heads, rec.kv_heads, rec.dim, rec.vdim, rec.scale = self.heads, 1, self.dim, self.vdim, self.scale
+        rec.q_rank, rec.kv_rank = self.q_rank, self.kv_rank
+        rec.q_lat_norm, rec.kv_lat_norm = self.q_lat_norm.data_ptr(), self.kv_lat_norm.data_ptr()
+        rec.w_uq, rec.w_uk_t, rec.w_uv = self.w_uq.data_ptr(), self.w_uk_t.data_ptr(), self.w_uv.data_ptr()
+        rec.sink = self.sink.data_ptr() if self.sink is not None else None
+        rec.latent_pages = st.latent_pages.data_ptr()
+
+
+class MLstm:
+    kind = "mlstm"
+
+    def __init__(self, w_q, w_k, w_v, w_i, w_f, w_gate, w_o, head_norm, *, heads: int, dim: int, vdim: int, gate_cap: float,
+                 b_i=None, b_f=None, device=None):
+        self.heads, self.dim, self.vdim, self.gate_cap = int(heads), int(dim), int(vdim), float(gate_cap)
+        if (tuple(w_q.shape)[0] != heads * dim or tuple(w_k.shape)[0] != heads * dim or tuple(w_v.shape)[0] != heads * vdim
+                or tuple(w_i.shape)[0] != heads or tuple(w_f.shape)[0] != heads or tuple(w_gate.shape)[0] != heads * vdim):
+            raise ValueError("projection shapes do not match heads x dim")
+        self.in_rows, self.w_o = [w_q, w_k, w_v, w_i, w_f, w_gate], w_o
+        zeros = lambda n: torch.zeros(n, dtype=torch.float32)    # noqa: E731
+        self.in_bias = None
+        if b_i is not None or b_f is not None:
+            self.in_bias = [zeros(2 * heads * dim + heads * vdim), b_i if b_i is not None else zeros(heads),
+                            b_f if b_f is not None else zeros(heads), zeros(heads * vdim)]
+        self.head_norm = _f32(head_norm, device)                 # [heads * vdim]
+
+    def state_spec(self) -> StateSpec:
+        # the normaliser rides as one more value column of the matrix state; the running maximum per head beside it
+        return StateSpec(recurrent=(self.heads, self.vdim + 1, self.dim), aux=self.heads)
+
+    def fill(self, rec, st) -> None:
+        from ._lm_lib import MIXER_MLSTM
+        rec.mixer = MIXER_MLSTM
+        rec.heads, rec.kv_heads, rec.dim, rec.vdim, rec.gate_cap = self.heads, self.heads, self.dim, self.vdim, self.gate_cap
+        rec.head_norm = self.head_norm.data_ptr()
+        rec.rec_state, rec.rec_aux = st.rec_state.data_ptr(), st.rec_aux.data_ptr()
+
+
+class GatedUnit:
+    def __init__(self, w_gate, w_up, w_down, *, limit: float | None, device=None):
+        """``down(act(gate h, up h))``; with ``limit`` the clamped activation, without it silu(g) u."""
+        self.ff, self.limit = int(w_gate.shape[0]), None if limit is None else float(limit)
+        self.w_gate_up, self.w_down = _bf16(torch.cat([w_gate, w_up], dim=0), device), _bf16(w_down, device)
+
+
+class StreamLayer:
+    """Pre-norm sublayers over hyper-connected residual streams: for the mixer and then the feed-forward,
+    ``u = sum_s in[s] x_s;  y = sublayer(layernorm(u) w);  x_j <- sum_s mix[s, j] x_s + out[j] y``.  Every projection that
+    reads the mixer's input is one stacked matrix.  The same object may stand in several layer records (a layer that runs
+    with another layer's weights): each record gets a state of its own."""
+
+    def __init__(self, norm1, hc1: HyperConnection, mixer, ff=None, norm2=None, hc2: HyperConnection | None = None, device=None):
+        self.mixer, self.ff, self.hc1, self.hc2 = mixer, ff, hc1, hc2
+        self.norm1 = _f32(norm1, device)
+        self.norm2 = None if norm2 is None else _f32(norm2, device)
+        if ff is not None and (norm2 is None or hc2 is None or hc2.streams != hc1.streams):
+            raise ValueError("a feed-forward sublayer needs its norm and hyper-connection weights")
+        rows = [_bf16(r, device) for r in mixer.in_rows]
+        n = sum(int(r.shape[0]) for r in rows)
+        self.n_in = (n + 3) & ~3
+        if self.n_in > n:
+            rows.append(torch.zeros((self.n_in - n, int(rows[0].shape[1])), dtype=torch.bfloat16, device=device))
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.in_bias = None
+        if mixer.in_bias is not None:
+            b = torch.cat([_f32(x, device).reshape(-1) for x in mixer.in_bias])
+            self.in_bias = torch.cat([b, torch.zeros(self.n_in - b.numel(), dtype=torch.float32, device=device)]).contiguous()
+        self.w_o = _bf16(mixer.w_o, device)
+
+    def state_spec(self) -> StateSpec:
+        return self.mixer.state_spec()
+
+    def fill(self, rec, st) -> None:
+        from ._lm_lib import (ACT_CLAMPED_GLU, ACT_SILU_GLU, FF_DENSE, FF_NONE, FF_ROUTED_EXPERTS, FORM_STREAMS, NORM_LAYER,
+                              ROUTER_SIGMOID_INPUT, ROUTER_SOFTMAX_TOP)
+        rec.form, rec.streams = FORM_STREAMS, self.hc1.streams
+        rec.norm_mix_in.w, rec.norm_mix_in.b, rec.norm_mix_in.kind = self.norm1.data_ptr(), None, NORM_LAYER
+        for q, hc in enumerate((self.hc1, self.hc2)):
+            if hc is not None:
+                rec.hc_in[q], rec.hc_out[q], rec.hc_mix[q] = hc.w_in.data_ptr(), hc.w_out.data_ptr(), hc.w_mix.data_ptr()
+        self.mixer.fill(rec, st)
+        rec.n_in, rec.w_in, rec.w_o = self.n_in, self.w_in.data_ptr(), self.w_o.data_ptr()
+        rec.in_bias = self.in_bias.data_ptr() if self.in_bias is not None else None
+        rec.ff = FF_NONE
+        f = self.ff
+        if f is None:
+            return
+        rec.norm_ff_in.w, rec.norm_ff_in.b, rec.norm_ff_in.kind = self.norm2.data_ptr(), None, NORM_LAYER
+        rec.act = ACT_CLAMPED_GLU if f.limit is not None else ACT_SILU_GLU
+        rec.act_limit = f.limit if f.limit is not None else 0.0
+        if isinstance(f, GatedUnit):
+            rec.ff, rec.dense_ff = FF_DENSE, f.ff
+            rec.ws_gate_up, rec.ws_down = f.w_gate_up.data_ptr(), f.w_down.data_ptr()
+            return
+        rec.ff = FF_ROUTED_EXPERTS
+        rec.experts, rec.top, rec.expert_ff, rec.shared_ff = f.experts, f.top, f.ff, f.shared_ff
+        rec.router = ROUTER_SOFTMAX_TOP if f.softmax_top else ROUTER_SIGMOID_INPUT
+        rec.router_bias = f.router_bias.data_ptr() if f.router_bias is not None else None
+        rec.shared_limit = f.shared_limit if f.shared_limit is not None else 0.0
+        rec.w_router, rec.w_gate_up, rec.w_down = f.w_router.data_ptr(), f.w_gate_up.data_ptr(), f.w_down.data_ptr()
+        if f.shared_ff:
+            rec.ws_gate_up, rec.ws_down = f.ws_gate_up.data_ptr(), f.ws_down.data_ptr()

@@ -18,10 +18,11 @@ from pathlib import Path
 import torch
 
 from .checkpoint import load_safetensors
-from .lm_config import KupelixConfig, PubopelConfig, load_config
+from .lm_config import KupelixConfig, LuketarConfig, PubopelConfig, load_config
 from .lm_engine import LMEngine
-from .lm_layers import (ChannelDelta, DenseXielu, DynamicTanh, Hgrn2, LayerNorm, LayerRun, MixLayer, ParallelLayer, RoutedExperts,
-                        SinkAttention, TalkingAttention, TapMix, rotary_angles)
+from .lm_layers import (ChannelDelta, DenseXielu, DynamicTanh, GatedUnit, Hgrn2, HyperConnection, LatentAttention, LayerNorm,
+                        LayerRun, MixLayer, MLstm, ParallelLayer, RoutedExperts, SinkAttention, StreamLayer, TalkingAttention,
+                        TapMix, rotary_angles)
 from .lm_state import OutOfPages, PagedState, Sequence
 
 
@@ -86,6 +87,51 @@ def build_kupelix_layers(cfg: KupelixConfig, w: dict[str, torch.Tensor], device)
     pre = w["loop.in"] if cfg.loop is not None else None
     runs = [LayerRun(built[i], pre if starts else None, device) for i, starts in cfg.runs()]
     return runs, LayerNorm(w["final.norm"], w["final.norm.b"], device)
+
+
+def build_luketar_layers(cfg: LuketarConfig, w: dict[str, torch.Tensor], device) -> tuple[list[StreamLayer], LayerNorm]:
+    """The layer records of a Luketar checkpoint in execution order (tensor names ``l<i>.norm1``, ``l<i>.hc1.in``,
+    ``l<i>.mix.*``, ``l<i>.mlp.*``): a layer with weights of its own is built once; a layer that names another layer's
+    weights is that layer's object again, and gets its own state record by its place in the list."""
+    built: dict[int, StreamLayer] = {}
+
+    def hyper(prefix: str) -> HyperConnection:
+        if cfg.streams is None:
+            return HyperConnection.residual(device)
+        return HyperConnection(w[prefix + "in"], w[prefix + "out"], w[prefix + "mix"], device)
+
+    def build(i: int) -> StreamLayer:
+        lc, p = cfg.layers[i], f"l{i}.mix."
+        m = lc.mixer
+        t = lambda name: w[p + name]                             # noqa: E731
+        if lc.type == "latent_attention":
+            mixer = LatentAttention(t("dq"), t("dq.norm"), t("uq"), t("dkv"), t("dkv.norm"), t("uk"), t("uv"), t("g"), t("o"),
+                                    heads=m.heads, dim=m.dim, vdim=m.vdim, scale=m.scale, sink=t("sink"), device=device)
+        else:
+            mixer = MLstm(t("q"), t("k"), t("v"), t("i"), t("f"), t("g"), t("o"), t("norm"), heads=m.heads, dim=m.dim,
+                          vdim=m.vdim, gate_cap=m.gate_cap, b_i=t("i.b"), b_f=t("f.b"), device=device)
+        ff = norm2 = hc2 = None
+        f, q = lc.mlp, f"l{i}.mlp."
+        if f is not None:
+            norm2, hc2 = w[f"l{i}.norm2"], hyper(f"l{i}.hc2.")
+            if f.kind == "dense":
+                ff = GatedUnit(w[q + "gate"], w[q + "up"], w[q + "down"], limit=f.limit, device=device)
+            else:
+                E = f.router.experts
+                shared = (w[q + "shared.gate"], w[q + "shared.up"], w[q + "shared.down"]) if f.shared is not None else None
+                ff = RoutedExperts(w[q + "router"], [w[q + f"e{e}.gate"] for e in range(E)], [w[q + f"e{e}.up"] for e in range(E)],
+                                   [w[q + f"e{e}.down"] for e in range(E)], top=f.router.top, shared=shared, device=device,
+                                   router_bias=w[q + "router.b"], softmax_top=True, limit=f.expert.limit,
+                                   shared_limit=f.shared.limit if f.shared is not None else None)
+        return StreamLayer(w[f"l{i}.norm1"], hyper(f"l{i}.hc1."), mixer, ff, norm2, hc2, device=device)
+
+    runs = []
+    for i in range(len(cfg.layers)):
+        j = cfg.weight_layer(i)
+        if j not in built:
+            built[j] = build(j)
+        runs.append(built[j])
+    return runs, LayerNorm(w["final.norm"], None, device)
 
 
 @dataclass
@@ -174,7 +220,7 @@ class Scheduler:
 
 
 class CausalLM:
-    def __init__(self, cfg: PubopelConfig | KupelixConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
+    def __init__(self, cfg: PubopelConfig | KupelixConfig | LuketarConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
                  max_tokens: int = 4096, max_sequences: int = 8, page_size: int = 16, max_rows: int = 1024,
                  max_sequence_tokens: int | None = None, step_graphs: bool = True):
         if dtype not in ("bfloat16", "float32"):
@@ -185,9 +231,14 @@ class CausalLM:
         self.config, self.dtype = cfg, dtype
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         # a design is its layer records (in execution order), its final norm and the constants around them
+        embed_scale, head = 1.0, weights.get("head")
         if isinstance(cfg, KupelixConfig):
             self.layers, final_norm = build_kupelix_layers(cfg, weights, self.device)
             taps, logit_scale = 0, cfg.logit_scale
+        elif isinstance(cfg, LuketarConfig):
+            self.layers, final_norm = build_luketar_layers(cfg, weights, self.device)
+            taps, logit_scale, embed_scale = 0, 1.0, cfg.embedding.scale
+            head = weights["embed"]                             # the logits are taken against the embedding table itself
         else:
             self.layers, final_norm = build_pubopel_layers(cfg, weights, self.device)
             taps, logit_scale = cfg.canon.taps, 1.0
@@ -196,9 +247,9 @@ class CausalLM:
         # float32: every product is fp32 arithmetic on the stored (bfloat16) weights.  bfloat16: the products of prompt
         # portions run on the tensor cores with bfloat16 operands and fp32 accumulation.  Norms, scores, the router, the
         # pages, recurrent states and the residual stream are float32 in both.
-        self.engine = LMEngine(self.layers, weights["embed"], weights["head"], final_norm, width=cfg.width, vocab=cfg.vocab,
+        self.engine = LMEngine(self.layers, weights["embed"], head, final_norm, width=cfg.width, vocab=cfg.vocab,
                                taps=taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype,
-                               step_graphs=step_graphs, logit_scale=logit_scale)
+                               step_graphs=step_graphs, logit_scale=logit_scale, embed_scale=embed_scale)
         self._draws = 0
 
     @classmethod

@@ -25,6 +25,8 @@ class StateSpec:
     tap_tails: int = 0                              # [taps - 1][width] tails of tap-mix sublayers
     recurrent: tuple[int, int, int] | None = None   # (heads, value size, key size): fp32 matrix state per slot
     conv: tuple[int, int] | None = None             # (taps, channels): the last taps - 1 inputs of a short convolution
+    latent: int | None = None                       # size of a paged latent vector per token (keys and values are made from it)
+    aux: int = 0                                    # fp32 numbers per slot beside a recurrent state (running maxima)
 
 
 class OutOfPages(RuntimeError):
@@ -47,6 +49,8 @@ class RecordState:
     tails: tuple
     rec_state: torch.Tensor | None
     conv_tail: torch.Tensor | None
+    latent_pages: torch.Tensor | None = None
+    rec_aux: torch.Tensor | None = None
 
 
 class PagedState:
@@ -78,6 +82,9 @@ class PagedState:
                            if sp.recurrent else None for sp in self.specs]
         self.conv_tails = [torch.zeros((self.n_slots, max(sp.conv[0] - 1, 1), sp.conv[1]), **f32) if sp.conv else None
                            for sp in self.specs]
+        # latent pages [page][page_size][size] share the page table with the K/V pages; per-slot numbers [slot][aux]
+        self.latent_pages = [torch.zeros((self.n_pages, self.page_size, sp.latent), **f32) if sp.latent else None for sp in self.specs]
+        self.rec_aux = [torch.zeros((self.n_slots, sp.aux), **f32) if sp.aux else None for sp in self.specs]
         self._table_host = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32).pin_memory() \
             if self.device.type == "cuda" else torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32)
         self.page_table = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32, device=self.device)
@@ -88,7 +95,8 @@ class PagedState:
 
     def record_state(self, i: int) -> "RecordState":
         """The buffers of layer record ``i`` (what its ``fill`` points the kernels at)."""
-        return RecordState(self.k_pages[i], self.v_pages[i], self.tails[i], self.rec_states[i], self.conv_tails[i])
+        return RecordState(self.k_pages[i], self.v_pages[i], self.tails[i], self.rec_states[i], self.conv_tails[i],
+                           self.latent_pages[i], self.rec_aux[i])
 
     # ---- bookkeeping -----------------------------------------------------------------------------------------
     @property

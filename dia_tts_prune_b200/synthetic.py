@@ -213,3 +213,82 @@ def kupelix_weights(cfg: dict, seed: int = 1234, device="cpu", rank: int = 64) -
             F = lc["mlp"]["ff"]
             w[p + "mlp.up"], w[p + "mlp.down"], w[p + "mlp.act"] = mat(F, D), mat(D, F), vec(2, 0.3, 0.3)
     return w
+
+
+def luketar_config(width: int, kinds: list[str], heads: int, dim: int, vdim: int, vocab: int, q_rank: int = 0, kv_rank: int = 0,
+                   ff: int = 0, experts: int = 0, top: int = 0, expert_ff: int = 0, shared_ff: int = 0, streams: int | None = None,
+                   repeat_last: bool = False) -> dict:
+    """A Luketar ``config.json`` as a dictionary: one layer per entry of ``kinds`` (``latent_attention`` / ``mlstm``), the
+    first with a dense gated unit of ``ff`` hidden units, the others with ``experts`` routed units (a dense one when
+    ``experts`` is 0); ``repeat_last`` appends a layer that runs with the last layer's weights."""
+    layers = []
+    for n, kind in enumerate(kinds):
+        m = {"heads": heads, "dim": dim, "vdim": vdim}
+        if kind == "latent_attention":
+            m.update(q_rank=q_rank, kv_rank=kv_rank, scale=dim ** -0.5)
+        else:
+            m.update(gate_cap=15.0)
+        if experts and n > 0:
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": top},
+                   "shared": {"ff": shared_ff, "limit": 7.0} if shared_ff else None}
+        else:
+            mlp = {"kind": "dense", "ff": ff, "limit": 7.0} if ff else None
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    if repeat_last:
+        layers.append(dict(layers[-1], weights_of=len(layers) - 1))
+    cfg = {"architecture": "Luketar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+           "layers": layers}
+    if streams:
+        cfg["streams"] = streams
+    return cfg
+
+
+def luketar_weights(cfg: dict, seed: int = 1234, device="cpu") -> dict:
+    """Random bfloat16 tensors under the checkpoint's names: matrices ~ N(0, 1 / fan_in), norms and stream weights near
+    the identity, forget gates mostly open."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, V, s = cfg["width"], cfg["vocab"], cfg.get("streams")
+
+    def mat(n, k, gain=1.0):
+        return (torch.randn((n, k), generator=g, device=device) * (gain * k ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, mean, spread):
+        return (mean + spread * torch.randn((n,), generator=g, device=device)).to(torch.bfloat16)
+
+    def unit(prefix, ff):
+        w[prefix + "gate"], w[prefix + "up"], w[prefix + "down"] = mat(ff, D), mat(ff, D), mat(D, ff)
+
+    w = {"embed": torch.randn((V, D), generator=g, device=device).to(torch.bfloat16), "final.norm": vec(D, 1.0, 0.05)}
+    for i, lc in enumerate(cfg["layers"]):
+        if lc.get("weights_of") is not None:
+            continue
+        p, m = f"l{i}.", lc["mixer"]
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        w[p + "norm1"] = vec(D, 1.0, 0.05)
+        if lc["type"] == "latent_attention":
+            rq, rk = m["q_rank"], m["kv_rank"]
+            w[p + "mix.dq"], w[p + "mix.dq.norm"], w[p + "mix.uq"] = mat(rq, D), vec(rq, 1.0, 0.05), mat(H * d, rq)
+            w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = mat(rk, D), vec(rk, 1.0, 0.05)
+            w[p + "mix.uk"], w[p + "mix.uv"], w[p + "mix.sink"] = mat(H * d, rk), mat(H * dv, rk), vec(H, 0.0, 0.5)
+        else:
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = mat(H * d, D), mat(H * d, D), mat(H * dv, D)
+            w[p + "mix.i"], w[p + "mix.f"] = mat(H, D), mat(H, D)
+            w[p + "mix.i.b"], w[p + "mix.f.b"], w[p + "mix.norm"] = vec(H, 0.0, 0.5), vec(H, 3.0, 1.0), vec(H * dv, 1.0, 0.05)
+        w[p + "mix.g"], w[p + "mix.o"] = mat(H * dv, D), mat(D, H * dv)
+        f = lc.get("mlp")
+        if f:
+            w[p + "norm2"] = vec(D, 1.0, 0.05)
+            if f["kind"] == "dense":
+                unit(p + "mlp.", f["ff"])
+            else:
+                for e in range(f["router"]["experts"]):
+                    unit(p + f"mlp.e{e}.", f["expert"]["ff"])
+                w[p + "mlp.router"], w[p + "mlp.router.b"] = mat(f["router"]["experts"], D), vec(f["router"]["experts"], 0.0, 0.2)
+                if f.get("shared"):
+                    unit(p + "mlp.shared.", f["shared"]["ff"])
+        if s:
+            for q in (1, 2) if f else (1,):
+                w[p + f"hc{q}.in"], w[p + f"hc{q}.out"] = vec(s, 1.0 / s, 0.05), vec(s, 1.0, 0.1)
+                w[p + f"hc{q}.mix"] = (torch.eye(s, device=device) + 0.1 * torch.randn((s, s), generator=g, device=device)).to(torch.bfloat16)
+    return w

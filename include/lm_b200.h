@@ -4,9 +4,12 @@
  * success or a negative code, nothing throws, a forward call neither allocates nor synchronises.  There is no CPU
  * fallback: every compute entry point launches kernels.
  *
- * A model is a stack of layer records.  A record has one of two forms:
+ * A model is a stack of layer records.  A record has one of three forms:
  *   sequential  x += norm_b(mixer(tapmix(norm_a(x))));  x += norm_b'(ff(tapmix'(norm_a'(x))))
  *   parallel    h = norm_a(x);  x += mixer(h) + ff(h)
+ *   streams     s residual streams x_1 .. x_s (all equal to the embedding output at first, summed at the end); per sublayer
+ *               u = sum_s in[s] x_s;  y = sublayer(norm(u));  x_j <- sum_s mix[s][j] x_s + out[j] y   (hyper-connections;
+ *               s = 1 with unit weights is the plain pre-norm residual)
  * and the mechanisms (norm kind, mixer kind, feed-forward kind) are selected and parameterised per record, so a design
  * combines them as it needs.  A layer that a design runs several times with the same weights is several records that
  * share weight pointers and differ in their state pointers.  Matrices are bf16 [out][in]; vectors and scalars fp32.
@@ -29,7 +32,7 @@
 extern "C" {
 #endif
 
-#define LM_B200_ABI_VERSION 2
+#define LM_B200_ABI_VERSION 3
 
 enum lm_b200_status { LM_B200_OK = 0, LM_B200_EINVAL = -1, LM_B200_ECUDA = -2, LM_B200_ENOMEM = -3, LM_B200_EUNSUPPORTED = -5 };
 
@@ -37,12 +40,19 @@ enum lm_b200_mixer_kind {
     LM_B200_MIXER_SINK_ATTENTION = 1,   /* values = projected keys, whole-projection norms, window, distance bias, sink */
     LM_B200_MIXER_TALK_ATTENTION = 2,   /* biased q/k/v, per-head norms, rotary positions, scores mixed across heads, sink, gate */
     LM_B200_MIXER_HGRN2 = 3,            /* gated linear recurrence: the forget gate also sets the write strength */
-    LM_B200_MIXER_CHANNEL_DELTA = 4     /* gated delta rule with a decay per head and key channel, short convolutions */
+    LM_B200_MIXER_CHANNEL_DELTA = 4,    /* gated delta rule with a decay per head and key channel, short convolutions */
+    LM_B200_MIXER_LATENT_ATTENTION = 5, /* queries through a normed latent, keys / values up-projected from one cached normed latent, sink, elementwise gate */
+    LM_B200_MIXER_MLSTM = 6             /* matrix memory with exponential input gate, running maximum and normaliser */
 };
 enum lm_b200_ff_kind { LM_B200_FF_NONE = 0, LM_B200_FF_ROUTED_EXPERTS = 1, LM_B200_FF_DENSE = 2 };
 enum lm_b200_norm_kind { LM_B200_NORM_DYT = 0, LM_B200_NORM_LAYER = 1 };
-enum lm_b200_layer_form { LM_B200_FORM_SEQUENTIAL = 0, LM_B200_FORM_PARALLEL = 1 };
-enum lm_b200_act_kind { LM_B200_ACT_XIELU = 1 };
+enum lm_b200_layer_form { LM_B200_FORM_SEQUENTIAL = 0, LM_B200_FORM_PARALLEL = 1, LM_B200_FORM_STREAMS = 2 };
+/* XIELU: up, activation, down.  SILU_GLU / CLAMPED_GLU: gated units [gate | up] -> down with silu(g) u, or with
+ * g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1) */
+enum lm_b200_act_kind { LM_B200_ACT_SILU_GLU = 0, LM_B200_ACT_XIELU = 1, LM_B200_ACT_CLAMPED_GLU = 2 };
+/* SIGMOID_INPUT: score sigmoid(z) multiplies the chosen expert's input.  SOFTMAX_TOP: the softmax over the chosen logits
+ * alone weighs the experts' outputs */
+enum lm_b200_router_kind { LM_B200_ROUTER_SIGMOID_INPUT = 0, LM_B200_ROUTER_SOFTMAX_TOP = 1 };
 /* FP32: every product is fp32 FMA arithmetic on the stored weights.  BF16: the products of a long step (a prompt portion)
  * run on the tensor cores with bf16 operands and fp32 accumulation; everything else stays fp32. */
 enum lm_b200_precision { LM_B200_PRECISION_FP32 = 0, LM_B200_PRECISION_BF16 = 1 };
@@ -101,6 +111,27 @@ typedef struct lm_b200_layer {
     const void *w_a2, *w_g2;       /* bf16 [heads*dim][rank_a], [heads*vdim][rank_g]: second steps of the decay and gate projections (fp32 arithmetic) */
     float *rec_state;              /* [slots][heads][vdim][dim] recurrent state per sequence (column of a value channel contiguous) */
     float *conv_tail;              /* [slots][conv_taps - 1][2 kv_heads*dim + heads*vdim] last projected inputs per sequence */
+
+    /* ---- the stream form and its mechanisms (all zero / NULL in the other forms) ----
+     * norm_mix_in / norm_ff_in: layer norms (weight; bias NULL) of the two sublayers.  w_in stacks every projection that
+     * reads the mixer's input, [n_in][width] (in_bias as above):
+     *   LATENT_ATTENTION  query latent (q_rank) | key/value latent (kv_rank) | gate (heads*vdim)
+     *   MLSTM             q (heads*dim) | k (heads*dim) | v (heads*vdim) | input gate (heads) | forget gate (heads) | gate (heads*vdim)
+     * w_o [width][heads*vdim] is the output projection.  Feed-forward: FF_DENSE is one gated unit (ws_gate_up / ws_down with
+     * dense_ff hidden units and act_limit); FF_ROUTED_EXPERTS as above with router, router_bias, act and the two limits. */
+    int32_t streams;               /* residual streams s, 1 .. 8 */
+    const float *hc_in[2], *hc_out[2], *hc_mix[2]; /* per sublayer (0 mixer, 1 feed-forward): [s], [s], [s][s] indexed [from][to] */
+    int32_t q_rank, kv_rank;       /* sizes of the query latent and of the cached key/value latent */
+    const float *q_lat_norm, *kv_lat_norm; /* [q_rank], [kv_rank] RMS norm weights of the latents */
+    const void *w_uq;              /* [heads*dim][q_rank] */
+    const void *w_uk_t;            /* [heads][kv_rank][dim]: per head the TRANSPOSED key up-projection: q_h is carried into the latent space */
+    const void *w_uv;              /* [heads][vdim][kv_rank] */
+    float *latent_pages;           /* [pages][page_size][kv_rank] */
+    float gate_cap;                /* mLSTM: gate pre-activations z become cap tanh(z / cap) */
+    float *rec_aux;                /* [slots][heads] running maxima of the stabilised recurrence (rec_state: [slots][heads][vdim + 1][dim]) */
+    int32_t router;                /* lm_b200_router_kind */
+    const float *router_bias;      /* [experts] added to the router logits; NULL: none */
+    float act_limit, shared_limit; /* clamps of a CLAMPED_GLU: routed experts / dense unit, shared expert */
 } lm_b200_layer;
 
 typedef struct lm_b200_model {
@@ -113,6 +144,7 @@ typedef struct lm_b200_model {
     const int32_t *page_table;     /* device, [n_slots][max_pages] */
     int32_t step_graphs;           /* != 0: steps of a few rows (decoding) replay a CUDA graph captured at their first use */
     float logit_scale;             /* multiplies the logits (0 is read as 1) */
+    float embed_scale;             /* multiplies the embedding rows (0 is read as 1) */
 } lm_b200_model;
 
 typedef struct lm_b200_engine lm_b200_engine;
