@@ -77,7 +77,7 @@ def latent_attention(h, p, m, eps):
     return (out.reshape(T, H * dv) * gate) @ p["o"].T
 
 
-def mlstm(h, p, m, eps):
+def mlstm(h, p, m, eps, m0=0.0, floor=True):
     """Matrix-memory recurrence with exponential input gate and a running maximum that starts at 0.  Per head:
     m_t = max(f_t + m_(t-1), i_t);  S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T;  n_t the same with
     k_t alone;  o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)."""
@@ -92,14 +92,15 @@ def mlstm(h, p, m, eps):
     for hh in range(H):
         S = torch.zeros((d, dv), dtype=h.dtype)
         n = torch.zeros((d,), dtype=h.dtype)
-        mx = torch.zeros((), dtype=h.dtype)
+        mx = torch.full((), m0, dtype=h.dtype)
         for t in range(T):
             new = torch.maximum(fg[t, hh] + mx, ig[t, hh])
             a, b = torch.exp(fg[t, hh] + mx - new), torch.exp(ig[t, hh] - new)
             S = a * S + b * torch.outer(k[t, hh], v[t, hh])
             n = a * n + b * k[t, hh]
             mx = new
-            den = torch.maximum(torch.abs(n @ q[t, hh]), torch.exp(-mx)) + 1e-6
+            nq = torch.abs(n @ q[t, hh])
+            den = (torch.maximum(nq, torch.exp(-mx)) if floor else nq) + 1e-6
             out[t, hh] = (S.T @ q[t, hh]) / den
     o = rms_unit(out, eps).reshape(T, H * dv) * p["norm"]
     return (o * torch.sigmoid(h @ p["g"].T)) @ p["o"].T
@@ -149,7 +150,7 @@ def forward(cfg, w, tokens, dtype=torch.float64, keep_layers=False):
     eps = cfg["norm"]["eps"]
     s = cfg.get("streams")
     embed = w["embed"].to(dtype)
-    x = embed[torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
+    x = embed[torch.as_tensor(tokens, dtype=torch.long)] * cfg.get("embedding", {}).get("scale", 1.0)
     X = x[:, None, :].repeat(1, s, 1) if s else None
     kept = []
 
@@ -178,6 +179,9 @@ def forward(cfg, w, tokens, dtype=torch.float64, keep_layers=False):
         x = X.sum(dim=1)
     logits = layer_norm_w(x, w["final.norm"].to(dtype), eps) @ embed.T
     return (logits, torch.stack(kept)) if keep_layers else logits
+
+
+MIXERS = {"latent_attention": latent_attention, "mlstm": mlstm}
 
 
 def greedy(cfg, w, prompt, n_new, dtype=torch.float64):
