@@ -21,7 +21,8 @@ path); `value` is the sum over ranks divided by the slowest rank's time (weak sc
 
 `--lm` leaves that workload aside and measures the decoder-only language-model path (Pubopel, random weights) at layer
 sizes of a real model: prefill and decode throughput through `CausalLM`, and its GEMM / attention kernels beside Dia's
-at equal size (one JSON line, metric `lm_layer_throughput`).  `--lm --lm-design kupelix` measures the Kupelix design
+at equal size (one JSON line, metric `lm_layer_throughput`).  `--lm --lm-design luketar` measures the Luketar design
+beside Kupelix and Pubopel at equal width and its mixers beside Kupelix's.  `--lm --lm-design kupelix` measures the Kupelix design
 instead: its prefill and decode throughput beside Pubopel's at equal width, heads and vocabulary, its attention kernel
 beside Pubopel's on the same causal workload, and its recurrence kernels against the bytes and state updates they must move.
 """
@@ -819,6 +820,129 @@ def run_lm_kupelix(args) -> None:
                       "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
 
 
+# ---- --lm --lm-design luketar: the Luketar design beside Kupelix and Pubopel at equal width, its mixers beside Kupelix's -----
+LUKETAR_SIZES = {
+    # the widths, head counts and vocabularies of LM_SIZES / KUPELIX_SIZES; a dense gated unit in the first layer and
+    # Pubopel's expert sizes in the others; the cached latent is as wide as two of Kupelix's four key heads
+    "w2048": dict(width=2048, kinds=["latent_attention", "mlstm", "latent_attention", "latent_attention"], heads=16, dim=128, vdim=128,
+                  q_rank=768, kv_rank=256, ff=4096, experts=8, top=2, expert_ff=2048, shared_ff=4096, vocab=32768, streams=4),
+    "w1024": dict(width=1024, kinds=["latent_attention", "mlstm", "latent_attention", "latent_attention"], heads=8, dim=128, vdim=128,
+                  q_rank=384, kv_rank=128, ff=1024, experts=16, top=2, expert_ff=512, shared_ff=1024, vocab=16384, streams=4),
+}
+
+
+def run_lm_luketar(args) -> None:
+    import torch
+    from dia_tts_prune_b200 import synthetic as SY
+    from dia_tts_prune_b200.lm_config import KupelixConfig, LuketarConfig, PubopelConfig
+    from dia_tts_prune_b200.lm_engine import launch_count
+    from dia_tts_prune_b200.lm_model import CausalLM
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        hbm, tf, src = float(pk["hbm_gbs"]), float(pk["bf16_tflops"]), "measured"
+    except Exception:
+        hbm, tf, src = 6650.0, 1590.0, "fallback"
+    flush = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)             # > the 126 MB L2
+    W, K = max(args.warmup, 3), max(args.steps, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    out = {}
+    T, ctx, R = args.lm_prompt, args.lm_context, args.lm_rows
+    for name in (args.lm_sizes.split(",") if args.lm_sizes else LUKETAR_SIZES):
+        sz, ksz, psz = LUKETAR_SIZES[name], KUPELIX_SIZES[name], LM_SIZES[name]
+        D, H, d, dv, V = sz["width"], sz["heads"], sz["dim"], sz["vdim"], sz["vocab"]
+        rq, rk, s = sz["q_rank"], sz["kv_rank"], sz["streams"]
+        toks = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(7)).tolist()
+        cap = max(T, 8 * (ctx + 32 * (K + 2))) + 64
+        res = {"config": sz}
+        kw = dict(dtype="bfloat16", device=dev, max_tokens=cap, max_sequences=8, page_size=64, max_rows=R)
+        cfg = SY.luketar_config(**sz)
+        model = CausalLM(LuketarConfig.model_validate(cfg), SY.luketar_weights(cfg, WEIGHT_SEED, dev), **kw)
+        res["luketar"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        kinds = sz["kinds"]
+        n_att, L = kinds.count("latent_attention"), len(kinds)
+        # products per token: stacked input projections, latent up-projections (the key / value ones per head in the latent
+        # space), output projection, active feed-forward units
+        att_cols = D * (rq + rk + H * dv) + rq * H * d + H * d * rk + H * rk * dv + H * dv * D
+        mem_cols = D * (2 * H * d + 2 * H * dv + 2 * H) + H * dv * D
+        ff_cols = [3 * D * sz["ff"]] + [3 * D * (sz["top"] * sz["expert_ff"] + sz["shared_ff"]) + D * sz["experts"]] * (L - 1)
+        mix_cols = [att_cols if k == "latent_attention" else mem_cols for k in kinds]
+        flops = 2.0 * T * (sum(mix_cols) + sum(ff_cols)) + n_att * 4.0 * H * rk * T * (T + 1) / 2 + \
+            (L - n_att) * 4.0 * T * H * d * (dv + 1) + 2.0 * D * V
+        w_bytes = 2.0 * (sum(mix_cols) + sum(ff_cols) + D * V)
+        state_bytes = 4.0 * ctx * rk * n_att + 8.0 * H * d * (dv + 1) * (L - n_att) + 8.0 * 2 * L * s * D
+        res["luketar"]["prefill"].update(model_tflops=flops / res["luketar"]["prefill"]["ms"] / 1e9,
+                                         frac_of_bf16_peak=flops / res["luketar"]["prefill"]["ms"] / 1e9 / tf)
+        b1 = res["luketar"]["decode_b1"]
+        b1.update(algorithmic_bytes=w_bytes + state_bytes, gb_per_s=(w_bytes + state_bytes) / b1["ms_per_step"] / 1e6,
+                  frac_of_hbm_peak=(w_bytes + state_bytes) / b1["ms_per_step"] / 1e6 / hbm)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+        kcfg = SY.kupelix_config(**ksz)
+        model = CausalLM(KupelixConfig.model_validate(kcfg), SY.kupelix_weights(kcfg, WEIGHT_SEED, dev), **kw)
+        res["kupelix"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+        pcfg = SY.pubopel_config(**psz)
+        model = CausalLM(PubopelConfig.model_validate(pcfg), SY.pubopel_weights(pcfg, WEIGHT_SEED, dev), **kw)
+        res["pubopel"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+
+        # -- mixers alone (projections, kernels, output projection; no feed-forward): one-layer models of either design
+        def timed(m1, n_seq, rows_each, start):
+            h = torch.randn(n_seq * min(rows_each, R), D, device=dev)
+            seqs = [m1.state.open(f"s{i}") for i in range(n_seq)]
+            for sq in seqs:
+                m1.state.reserve(sq, start + rows_each)
+            def run():
+                for r0 in range(0, rows_each, R):
+                    n = min(R, rows_each - r0)
+                    m1.engine.op_mixer(0, h[:n_seq * n], [(sq, n, start + r0) for sq in seqs])
+            ms = _event_ms(run, 2, K, flush)
+            for i in range(n_seq):
+                m1.state.close(f"s{i}")
+            return ms
+
+        kw1 = dict(dtype="bfloat16", device=dev, max_tokens=8 * T + 64, max_sequences=8, page_size=64, max_rows=R)
+        mixers = {}
+        for kind, twin in (("latent_attention", "attention"), ("mlstm", "hgrn2")):
+            c1 = SY.luketar_config(**{**sz, "kinds": [kind], "vocab": 256, "ff": 0, "experts": 0})
+            m1 = CausalLM(LuketarConfig.model_validate(c1), SY.luketar_weights(c1, 3, dev), **kw1)
+            k1 = SY.kupelix_config(**{**ksz, "kinds": [twin], "vocab": 256, "ff": 8})
+            m2 = CausalLM(KupelixConfig.model_validate(k1), SY.kupelix_weights(k1, 3, dev), **kw1)
+            ent = {}
+            for label, (n_seq, rows_each, start) in {"prefill_1x%d" % T: (1, T, 0), "decode_b8": (8, 1, ctx)}.items():
+                ent[label] = {"luketar_ms": timed(m1, n_seq, rows_each, start), "kupelix_" + twin + "_ms": timed(m2, n_seq, rows_each, start)}
+            if kind == "latent_attention":
+                ent["prefill_1x%d" % T].update(luketar_attention_flops=4.0 * H * rk * T * (T + 1) / 2,
+                                               kupelix_attention_flops=2.0 * H * (d + dv) * T * (T + 1) / 2)
+                ent["decode_b8"].update(luketar_cache_bytes=8.0 * ctx * rk * 4, kupelix_cache_bytes=8.0 * ctx * ksz["kv_heads"] * (d + dv) * 4)
+            mixers[kind] = ent
+            m1.engine.close()
+            m2.engine.close()
+            del m1, m2
+            torch.cuda.empty_cache()
+        res["mixers"] = mixers
+        out[name] = res
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "lm_layer_throughput", "design": "luketar", "impl": "ours", "n_gpus": 1, "steps": K, "warmup": W,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids)",
+                      "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+                      "timing": "CUDA events, median; a 160 MB buffer is rewritten between timed iterations (L2 flush)",
+                      "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -841,15 +965,16 @@ def main():
     ap.add_argument("--lm", action="store_true",
                     help="instead of the headline workload: prefill / decode throughput of the decoder-only language-model path "
                          "(Pubopel, random weights) at layer sizes of a real model, beside Dia's kernels at equal size")
-    ap.add_argument("--lm-design", default="pubopel", choices=["pubopel", "kupelix"],
-                    help="--lm: the design that is measured (kupelix: beside Pubopel at equal width, and its kernels beside Pubopel's)")
+    ap.add_argument("--lm-design", default="pubopel", choices=["pubopel", "kupelix", "luketar"],
+                    help="--lm: the design that is measured (kupelix: beside Pubopel at equal width, and its kernels beside Pubopel's; "
+                         "luketar: beside Kupelix and Pubopel at equal width, and its mixers beside Kupelix's)")
     ap.add_argument("--lm-sizes", default="", help="--lm: comma-separated subset of " + ",".join(LM_SIZES))
     ap.add_argument("--lm-prompt", type=int, default=4096, help="--lm: prompt tokens of the prefill measurement")
     ap.add_argument("--lm-rows", type=int, default=4096, help="--lm: most rows of one engine step (longer prompts run in portions)")
     ap.add_argument("--lm-context", type=int, default=1024, help="--lm: tokens each sequence holds before the decode measurement")
     args = ap.parse_args()
     if args.lm:
-        (run_lm_kupelix if args.lm_design == "kupelix" else run_lm)(args)
+        {"kupelix": run_lm_kupelix, "luketar": run_lm_luketar}.get(args.lm_design, run_lm)(args)
         return
     if args.impl == "reference":
         run_reference(args)

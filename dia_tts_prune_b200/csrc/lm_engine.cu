@@ -252,7 +252,7 @@ int check_stream_layer(const lm_b200_model& m, const lm_b200_layer& l) {
             break;
         case LM_B200_MIXER_MLSTM:
             if (!l.head_norm || !l.rec_state || !l.rec_aux || !(l.gate_cap > 0.f)) return LM_B200_EINVAL;
-            if (l.dim > 256 || l.heads > 256) return LM_B200_EUNSUPPORTED;
+            if (l.dim > 256 || l.heads > 65535) return LM_B200_EUNSUPPORTED;
             break;
         default: return LM_B200_EUNSUPPORTED;
     }

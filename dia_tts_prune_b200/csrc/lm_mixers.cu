@@ -198,6 +198,9 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     // later rows see more keys: their tiles start first
     const int r0 = (gridDim.x - 1 - blockIdx.x) * TQ, n_rows = min(TQ, M - r0), S = gridDim.y, sp = blockIdx.y;
     const bool vec_q = (dim % 4 == 0) && (ld % 4 == 0) && (q_off % 4 == 0), vec_k = dim % 4 == 0, vec_v = vdim % 4 == 0;
+    // one key/value head whose value pages ARE its key pages (attention over a cached latent): the key tile of a stage
+    // serves as its value tile, so a tile of keys is one gather and stays in its buffer through both phases
+    const bool shared_kv = kcache == vcache && G == 1 && dim == vdim;
 
     if (tid < TQ) {
         s_slot[tid] = tid < n_rows ? row_slot[r0 + tid] : -1;
@@ -265,10 +268,14 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                 }
             }
             const bool is_k = ph < G;
+            if (shared_kv && !is_k) {
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                return;
+            }
             const int g = is_k ? ph : ph - G, width = is_k ? dim : vdim, W4 = is_k ? D4 : (SV >> 2);
             const float* cache = is_k ? kcache : vcache;
             const bool vec = is_k ? vec_k : vec_v;
-            float* dstb = KVs + (stg & 1) * TK * kv_stride;
+            float* dstb = KVs + ((shared_kv ? tile : stg) & 1) * TK * kv_stride;
             for (int c4 = lane; c4 < W4; c4 += 32) {
                 const int c = c4 * 4;
 #pragma unroll
@@ -303,7 +310,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();                                  // stage stg has landed; stage stg - 1 is consumed
             if (stg + 1 < n_stage) gather(stg + 1);
-            const float* KV = KVs + (stg & 1) * TK * kv_stride;
+            const float* KV = KVs + ((shared_kv ? tile : stg) & 1) * TK * kv_stride;
             if (ph < G) {
                 // ---- A: raw scores of the heads that read key/value head g ----
                 const int g = ph;

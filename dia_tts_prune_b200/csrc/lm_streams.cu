@@ -14,8 +14,8 @@
 //                             the pages: the latent is all an attention layer of this kind caches)
 //   head_linear_*_kernel      per-head products Y[m][h] = alpha A[m][h] . W[h]^T with an optional sigmoid gate: queries
 //                             into the latent space (q_h^T W_uk,h) and attended latents out of it (W_uv,h o_h)
-//   mlstm_gates_kernel        capped log-space input / forget gates and the running maximum m along a sequence's rows ->
-//                             decay exp(f + m' - m), write strength exp(i - m), floor exp(-m) per (row, head)
+//   mlstm_gates_kernel        capped log-space input / forget gates and the running maximum m along a sequence's rows (a
+//                             max-plus warp scan) -> decay exp(f + m' - m), write strength exp(i - m), floor exp(-m)
 //   mlstm_finish_kernel       read-out / (max(|n . q|, floor) + 1e-6), per-head RMS norm, weight, sigmoid gate
 //
 // The attention itself is talk_attention_kernel of lm_mixers.cu with ONE key/value head whose key and value pages are
@@ -49,13 +49,14 @@ __global__ void streams_embed_kernel(const __nv_bfloat16* __restrict__ table, co
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One CTA per (output) row.  X [M][streams][D].
+// One CTA per (output) row.  X [M][streams][D].  VW = 4: D is a multiple of 4 and every row is moved in 16-byte pieces.
+template <int VW>
 __global__ void __launch_bounds__(256)
 streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict__ mix, const float* __restrict__ out,
                     const float* __restrict__ y, const float* __restrict__ parts, const int* __restrict__ slot_of,
                     const float* __restrict__ sel_w, int top, const float* __restrict__ in, const float* __restrict__ norm_w,
                     float eps, const int* __restrict__ rows, float* __restrict__ h, __nv_bfloat16* __restrict__ h_b, int D) {
-    extern __shared__ float u_s[];                            // [D]
+    extern __shared__ __align__(16) float u_s[];              // [D]
     __shared__ float red[32];
     __shared__ float mix_s[kMaxStreams * kMaxStreams], out_s[kMaxStreams], in_s[kMaxStreams];
     pdl_release();
@@ -70,48 +71,86 @@ streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict_
     __syncthreads();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = X + (size_t)r * s * D;
+    auto load = [](const float* p, float (&v)[VW]) {
+        if (VW == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(p);
+            v[0] = t.x; v[1 % VW] = t.y; v[2 % VW] = t.z; v[3 % VW] = t.w;
+        } else {
+            v[0] = *p;
+        }
+    };
+    auto store = [](float* p, const float (&v)[VW]) {
+        if (VW == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1 % VW], v[2 % VW], v[3 % VW]);
+        else *p = v[0];
+    };
     float sum = 0.f;
-    for (int c = tid; c < D; c += blockDim.x) {
-        float xs[kMaxStreams];
+    for (int c = tid * VW; c < D; c += blockDim.x * VW) {
+        float xs[kMaxStreams][VW];
 #pragma unroll
-        for (int j = 0; j < kMaxStreams; ++j) xs[j] = j < s ? xr[(size_t)j * D + c] : 0.f;
+        for (int j = 0; j < kMaxStreams; ++j) {
+            if (j < s) load(xr + (size_t)j * D + c, xs[j]);
+            else
+#pragma unroll
+                for (int e = 0; e < VW; ++e) xs[j][e] = 0.f;
+        }
         if (write) {
-            float yv = y ? y[(size_t)r * D + c] : 0.f;
+            float yv[VW];
+#pragma unroll
+            for (int e = 0; e < VW; ++e) yv[e] = 0.f;
+            if (y) load(y + (size_t)r * D + c, yv);
             if (parts)
-                for (int t = 0; t < top; ++t)
-                    yv = fmaf(sel_w[(size_t)r * top + t], parts[(size_t)slot_of[(size_t)r * top + t] * D + c], yv);
-            float nx[kMaxStreams];
+                for (int t = 0; t < top; ++t) {
+                    float pv[VW];
+                    load(parts + (size_t)slot_of[(size_t)r * top + t] * D + c, pv);
+                    const float wt = sel_w[(size_t)r * top + t];
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) yv[e] = fmaf(wt, pv[e], yv[e]);
+                }
+            float nx[kMaxStreams][VW];
 #pragma unroll
             for (int j = 0; j < kMaxStreams; ++j) {
-                float v = 0.f;
+#pragma unroll
+                for (int e = 0; e < VW; ++e) nx[j][e] = 0.f;
                 if (j < s) {
 #pragma unroll
                     for (int i = 0; i < kMaxStreams; ++i)
-                        if (i < s) v = fmaf(mix_s[i * s + j], xs[i], v);
-                    v = fmaf(out_s[j], yv, v);
-                    xr[(size_t)j * D + c] = v;
+                        if (i < s) {
+                            const float mw = mix_s[i * s + j];
+#pragma unroll
+                            for (int e = 0; e < VW; ++e) nx[j][e] = fmaf(mw, xs[i][e], nx[j][e]);
+                        }
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) nx[j][e] = fmaf(out_s[j], yv[e], nx[j][e]);
+                    store(xr + (size_t)j * D + c, nx[j]);
                 }
-                nx[j] = v;
             }
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j) xs[j] = nx[j];
-        }
-        float uv = 0.f;
+            for (int j = 0; j < kMaxStreams; ++j)
 #pragma unroll
-        for (int j = 0; j < kMaxStreams; ++j)
-            if (j < s) uv = fmaf(in_s[j], xs[j], uv);
+                for (int e = 0; e < VW; ++e) xs[j][e] = nx[j][e];
+        }
         if (h) {
-            u_s[c] = uv;
-            sum += uv;
+            float uv[VW];
+#pragma unroll
+            for (int e = 0; e < VW; ++e) uv[e] = 0.f;
+#pragma unroll
+            for (int j = 0; j < kMaxStreams; ++j)
+                if (j < s)
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) uv[e] = fmaf(in_s[j], xs[j][e], uv[e]);
+            store(u_s + c, uv);
+#pragma unroll
+            for (int e = 0; e < VW; ++e) sum += uv[e];
         }
     }
     if (!h) return;
-    if (!norm_w) {                                            // the plain read
-        __syncthreads();
-        for (int c = tid; c < D; c += blockDim.x) {
-            h[(size_t)blockIdx.x * D + c] = u_s[c];
-            if (h_b) h_b[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(u_s[c]);
-        }
+    if (!norm_w) {                                            // the plain read (every thread re-reads what it wrote itself)
+        for (int c = tid * VW; c < D; c += blockDim.x * VW)
+#pragma unroll
+            for (int e = 0; e < VW; ++e) {
+                h[(size_t)blockIdx.x * D + c + e] = u_s[c + e];
+                if (h_b) h_b[(size_t)blockIdx.x * D + c + e] = __float2bfloat16_rn(u_s[c + e]);
+            }
         return;
     }
     const float mean = block_sum(sum, red) / (float)D;
@@ -276,58 +315,50 @@ head_linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat1
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One CTA per scheduled sequence.  The sequence's rows go through shared memory in chunks: all threads turn the raw gate
-// columns into log-space gates, one thread per head walks the chunk in order (the running maximum is the only thing that
-// passes from row to row), all threads write decay, write strength and floor back.
-constexpr int kGateChunk = 2048;                              // (row, head) pairs per chunk
-
+// One warp per (scheduled sequence, head), 32 rows at a time.  m_t = max(f_t + m_(t-1), i_t) composes: a run of rows acts
+// on the incoming maximum as m -> max(F + m, I) with F the sum of its f and I = max over its rows of (i_t + the f after
+// it), and two runs combine as (F1 + F2, max(I1 + F2, I2)) - an inclusive warp scan gives every row its own (F, I).
 __device__ __forceinline__ float logsigmoidf_(float z) { return z < -20.f ? z : -log1pf(expf(-z)); }
 
 __global__ void __launch_bounds__(256)
 mlstm_gates_kernel(float* __restrict__ proj, int ld, int i_off, int f_off, const float* __restrict__ bias, float cap, int H,
                    float* __restrict__ m_state, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
                    const int* __restrict__ seq_count, const int* __restrict__ row_pos, float* __restrict__ floor_out) {
-    __shared__ float gi[kGateChunk], gf[kGateChunk], ge[kGateChunk];
     pdl_release();
     pdl_wait();
-    const int s = blockIdx.x, tid = threadIdx.x;              // H <= blockDim.x: thread h walks head h
+    const int s = blockIdx.x, lane = threadIdx.x & 31, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= H) return;
     const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s], start = row_pos[row0];
-    const int rows_per = kGateChunk / H;
-    float m = 0.f;                                            // the running maximum starts at 0 with the sequence
-    if (tid < H && start > 0) m = m_state[(size_t)slot * H + tid];
-    for (int t0 = 0; t0 < n; t0 += rows_per) {
-        const int nt = min(rows_per, n - t0);
-        __syncthreads();
-        for (int idx = tid; idx < nt * H; idx += blockDim.x) {
-            const int t = idx / H, h = idx - t * H;
-            const float* row = proj + (size_t)(row0 + t0 + t) * ld;
-            const float zi = row[i_off + h] + (bias ? bias[i_off + h] : 0.f);
-            const float zf = row[f_off + h] + (bias ? bias[f_off + h] : 0.f);
-            gi[idx] = cap * tanhf(zi / cap);
-            gf[idx] = logsigmoidf_(cap * tanhf(zf / cap));
+    const float bi = bias ? bias[i_off + h] : 0.f, bfg = bias ? bias[f_off + h] : 0.f;
+    float m_in = start > 0 ? m_state[(size_t)slot * H + h] : 0.f;     // the running maximum starts at 0 with the sequence
+    for (int t0 = 0; t0 < n; t0 += 32) {
+        const bool ok = t0 + lane < n;
+        float* row = proj + (size_t)(row0 + t0 + (ok ? lane : 0)) * ld;
+        float ig = -CUDART_INF_F, fg = 0.f;                   // beyond the last row: the identity (F = 0, I = -inf)
+        if (ok) {
+            ig = cap * tanhf((row[i_off + h] + bi) / cap);
+            fg = logsigmoidf_(cap * tanhf((row[f_off + h] + bfg) / cap));
         }
-        __syncthreads();
-        if (tid < H) {
-            for (int t = 0; t < nt; ++t) {
-                const int idx = t * H + tid;
-                const float i = gi[idx], f = gf[idx];
-                const float mn = fmaxf(f + m, i);
-                gi[idx] = expf(i - mn);                       // write strength
-                gf[idx] = expf(f + m - mn);                   // decay
-                ge[idx] = expf(-mn);                          // floor of the normaliser
-                m = mn;
+        float F = fg, I = ig;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float Fl = __shfl_up_sync(0xffffffffu, F, o), Il = __shfl_up_sync(0xffffffffu, I, o);
+            if (lane >= o) {
+                I = fmaxf(Il + F, I);
+                F = Fl + F;
             }
         }
-        __syncthreads();
-        for (int idx = tid; idx < nt * H; idx += blockDim.x) {
-            const int t = idx / H, h = idx - t * H;
-            float* row = proj + (size_t)(row0 + t0 + t) * ld;
-            row[i_off + h] = gi[idx];
-            row[f_off + h] = gf[idx];
-            floor_out[(size_t)(row0 + t0 + t) * H + h] = ge[idx];
+        const float m = fmaxf(F + m_in, I);
+        float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
+        if (lane == 0) m_prev = m_in;
+        if (ok) {
+            row[i_off + h] = expf(ig - m);                    // write strength
+            row[f_off + h] = expf(fg + m_prev - m);           // decay
+            floor_out[(size_t)(row0 + t0 + lane) * H + h] = expf(-m);
         }
+        m_in = __shfl_sync(0xffffffffu, m, 31);               // (lanes beyond the last row carry it on unchanged)
     }
-    if (tid < H) m_state[(size_t)slot * H + tid] = m;
+    if (lane == 0) m_state[(size_t)slot * H + h] = m_in;
 }
 
 // one warp per (row, head).  raw [M][H][vdim + 1]: the read-out and, in its last column, n . q
@@ -370,19 +401,22 @@ cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, co
                                 const int* rows, float* h, void* h_bf16, int M, int D, cudaStream_t st) {
     if (streams < 1 || streams > kMaxStreams) return cudaErrorNotSupported;
     const size_t smem = (size_t)D * 4;
-    static size_t allowed[64] = {};
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = D % 4 == 0 && aligned(X) && aligned(wr.y) && aligned(wr.parts);
+    auto kernel = vec ? streams_step_kernel<4> : streams_step_kernel<1>;
+    static size_t allowed[2][64] = {};
     if (smem > 48 * 1024) {
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);
         if (e != cudaSuccess) return e;
-        if (dev < 0 || dev >= 64 || allowed[dev] < smem) {
-            e = cudaFuncSetAttribute(streams_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (dev < 0 || dev >= 64 || allowed[vec][dev] < smem) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
-            if (dev >= 0 && dev < 64) allowed[dev] = smem;
+            if (dev >= 0 && dev < 64) allowed[vec][dev] = smem;
         }
     }
-    return launch_pdl(streams_step_kernel, dim3(M), dim3(256), smem, st, X, streams, wr.mix, wr.out, wr.y, wr.parts, wr.slot_of,
-                      wr.sel_w, wr.top, in, norm_w, eps, rows, h, reinterpret_cast<__nv_bfloat16*>(h_bf16), D);
+    return launch_pdl(kernel, dim3(M), dim3(256), smem, st, X, streams, wr.mix, wr.out, wr.y, wr.parts, wr.slot_of, wr.sel_w, wr.top,
+                      in, norm_w, eps, rows, h, reinterpret_cast<__nv_bfloat16*>(h_bf16), D);
 }
 
 cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* qw,
@@ -407,8 +441,8 @@ cudaError_t launch_head_linear(const float* A, int lda, const void* W, float* Y,
 
 cudaError_t launch_mlstm_gates(float* proj, int ld, int i_off, int f_off, const float* bias, float cap, int H, float* m_state,
                                const SeqMeta& sm, const RowMeta& rm, int n_seq, float* floor_out, cudaStream_t st) {
-    if (H > 256) return cudaErrorNotSupported;                // one thread per head walks the running maximum
-    return launch_pdl(mlstm_gates_kernel, dim3(n_seq), dim3(256), 0, st, proj, ld, i_off, f_off, bias, cap, H, m_state, sm.slot,
+    if (H > 8 * 65535) return cudaErrorNotSupported;
+    return launch_pdl(mlstm_gates_kernel, dim3(n_seq, (H + 7) / 8), dim3(256), 0, st, proj, ld, i_off, f_off, bias, cap, H, m_state, sm.slot,
                       sm.row0, sm.count, rm.pos, floor_out);
 }
 

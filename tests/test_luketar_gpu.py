@@ -185,7 +185,9 @@ def test_whole_prompt_logits_and_layer_streams(make):
     ref, streams = O.forward(cfg, w, toks, keep_layers=True)
     got, got_streams = whole(model, "a", toks, keep_layers=True)
     assert got_streams.shape[0] == len(cfg["layers"])
-    close(got_streams, streams, 2e-5)
+    # (how far the plain code itself lands in float32 arithmetic: small, ill-conditioned layers amplify rounding)
+    slack = (O.forward(cfg, w, toks, dtype=torch.float32, keep_layers=True)[1].double() - streams).abs().max().item()
+    close(got_streams, streams, 2e-5, slack)
     close(got, ref)
     for n in (1, 2, 3):                                         # the first tokens of a sequence
         close(whole(model, "b", toks[:n]), ref[:n])
