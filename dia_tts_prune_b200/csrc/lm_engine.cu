@@ -248,7 +248,8 @@ int check_stream_layer(const lm_b200_model& m, const lm_b200_layer& l) {
             if (l.q_rank <= 0 || l.kv_rank <= 0 || !l.q_lat_norm || !l.kv_lat_norm || !l.w_uq || !l.w_uk_t || !l.w_uv ||
                 !l.latent_pages)
                 return LM_B200_EINVAL;
-            if (!lm::talk_attention_supported(latent_shape(l))) return LM_B200_EUNSUPPORTED;
+            if (!lm::talk_attention_supported(latent_shape(l)) && !lm::latent_attention_rows_supported(l.heads, l.kv_rank))
+                return LM_B200_EUNSUPPORTED;
             break;
         case LM_B200_MIXER_MLSTM:
             if (!l.head_norm || !l.rec_state || !l.rec_aux || !(l.gate_cap > 0.f)) return LM_B200_EINVAL;
@@ -542,8 +543,11 @@ int stream_mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
         if (rc) return rc;
         // scores q_h . (W_uk,h c_j) = (W_uk,h^T q_h) . c_j: the query goes into the latent space, with the score multiplier
         LCK(lm::launch_head_linear(e->qk, nq, l.w_uk_t, e->qlat, nl, nullptr, M, H, l.kv_rank, l.dim, l.scale, nullptr, 0, st));
-        LCK(lm::launch_talk_attention(e->qlat, nl, 0, -1, l.latent_pages, l.latent_pages, pm, latent_shape(l), v.rm, e->olat, nl,
-                                      nullptr, e->split_ws, e->split_arrived, M, st));
+        if (lm::talk_attention_supported(latent_shape(l)))
+            LCK(lm::launch_talk_attention(e->qlat, nl, 0, -1, l.latent_pages, l.latent_pages, pm, latent_shape(l), v.rm, e->olat, nl,
+                                          nullptr, e->split_ws, e->split_arrived, M, st));
+        else
+            LCK(lm::launch_latent_attention_rows(e->qlat, l.latent_pages, pm, H, l.kv_rank, l.sink, v.rm, e->olat, M, st));
         // sum_j p_j (W_uv,h c_j) = W_uv,h (sum_j p_j c_j), times the sigmoid of the gate columns
         LCK(lm::launch_head_linear(e->olat, nl, l.w_uv, e->att, nv, bf ? e->attb : nullptr, M, H, l.vdim, l.kv_rank, 1.f,
                                    e->proj + c.gate, c.n, st));
@@ -675,7 +679,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
                 qk = std::max(qk, (size_t)l.heads * l.dim);
                 n_lat = std::max(n_lat, (size_t)l.heads * l.kv_rank);
                 q_rank = std::max(q_rank, (size_t)l.q_rank);
-                split_dim = std::max(split_dim, (size_t)l.heads * (l.kv_rank + 2));
+                if (lm::talk_attention_supported(latent_shape(l))) split_dim = std::max(split_dim, (size_t)l.heads * (l.kv_rank + 2));
             } else {
                 n_lat = std::max(n_lat, (size_t)l.heads * (l.vdim + 1));
             }

@@ -135,6 +135,11 @@ cudaError_t launch_streams_embed(const void* table_bf16, const int* ids, float s
 cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* qw,
                                const float* cw, float eps, void* cq_bf16, float* pages, const PageMap& pm, const RowMeta& rm,
                                int M, cudaStream_t st);
+// attention of every (row, head) over the latent pages on its own (keys = values = the cached latents; q [M][H][R] carries
+// the score multiplier): the fallback for shapes the tiled attention kernel does not take
+bool latent_attention_rows_supported(int H, int R);
+cudaError_t launch_latent_attention_rows(const float* q, const float* pages, const PageMap& pm, int H, int R, const float* sink,
+                                         const RowMeta& rm, float* out, int M, cudaStream_t st);
 // Y[m][h N + n] = alpha * sum_k A[m][h K + k] W[h][n][k]  [* sigmoid(gate[m][h N + n])], fp32 arithmetic on bf16 weights
 cudaError_t launch_head_linear(const float* A, int lda, const void* W, float* Y, int ldy, void* y_bf16, int M, int H, int N, int K,
                                float alpha, const float* gate, int ldg, cudaStream_t st);

@@ -12,6 +12,7 @@
 //                             write it is the first read of a step; without in / w it is the plain sum of the streams
 //   latent_prep_kernel        RMS norms of the query latent (in place, + bf16 operand) and of the key/value latent (into
 //                             the pages: the latent is all an attention layer of this kind caches)
+//   latent_attention_rows_kernel  attention over the latent pages for shapes the tiled kernel does not take
 //   head_linear_*_kernel      per-head products Y[m][h] = alpha A[m][h] . W[h]^T with an optional sigmoid gate: queries
 //                             into the latent space (q_h^T W_uk,h) and attended latents out of it (W_uv,h o_h)
 //   mlstm_gates_kernel        capped log-space input / forget gates and the running maximum m along a sequence's rows (a
@@ -194,6 +195,73 @@ latent_prep_kernel(float* __restrict__ proj, int ld, int q_off, int q_rank, int 
     const int page = table[(size_t)row_slot[r] * max_pages + pos / page_size];
     float* dst = pages + ((size_t)page * page_size + pos % page_size) * kv_rank;
     for (int c = tid; c < kv_rank; c += blockDim.x) dst[c] = row[c_off + c] * cinv * cw[c];
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention over the latent pages for shapes the tiled kernel does not take (latents wider than 256, more heads than a
+// tile holds): one CTA per (row, head), keys dealt to the warps in turn, every warp keeps its own running maximum,
+// denominator and weighted latent sum (lane l owns latent channels l, l + 32, ...), and the warps' shares are merged in
+// their fixed order with the sink's term.  q [M][H][R] carries the score multiplier; out [M][H][R].
+constexpr int kLatentPerLane = 32;                            // latent channels per lane: R <= 1024
+constexpr int kLatentWarps = 8;
+
+__global__ void __launch_bounds__(kLatentWarps * 32)
+latent_attention_rows_kernel(const float* __restrict__ q, const float* __restrict__ pages, const int* __restrict__ table,
+                             int max_pages, int page_size, int H, int R, const float* __restrict__ sink,
+                             const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out) {
+    extern __shared__ float sm[];                             // q [R] | per warp: sums [R], maximum, denominator
+    float* qs = sm;
+    float* part = sm + R;
+    pdl_release();
+    pdl_wait();
+    const int r = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = row_pos[r];
+    const int* pg = table + (size_t)row_slot[r] * max_pages;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) qs[c] = q[((size_t)r * H + h) * R + c];
+    __syncthreads();
+    float acc[kLatentPerLane];
+#pragma unroll
+    for (int u = 0; u < kLatentPerLane; ++u) acc[u] = 0.f;
+    float m = -CUDART_INF_F, l = 0.f;
+    for (int j = warp; j <= pos; j += kLatentWarps) {
+        const float* c = pages + ((size_t)pg[j / page_size] * page_size + j % page_size) * R;
+        float cv[kLatentPerLane], sc = 0.f;
+#pragma unroll
+        for (int u = 0; u < kLatentPerLane; ++u) {
+            const int ch = lane + 32 * u;
+            cv[u] = ch < R ? c[ch] : 0.f;
+            sc = fmaf(ch < R ? qs[ch] : 0.f, cv[u], sc);
+        }
+        sc = warp_sum(sc);
+        const float mn = fmaxf(m, sc), corr = expf(m - mn), p = expf(sc - mn);
+        l = fmaf(l, corr, p);
+#pragma unroll
+        for (int u = 0; u < kLatentPerLane; ++u) acc[u] = fmaf(acc[u], corr, p * cv[u]);
+        m = mn;
+    }
+    float* mine = part + (size_t)warp * (R + 2);
+#pragma unroll
+    for (int u = 0; u < kLatentPerLane; ++u)
+        if (lane + 32 * u < R) mine[lane + 32 * u] = acc[u];
+    if (lane == 0) { mine[R] = m; mine[R + 1] = l; }
+    __syncthreads();
+    const float sk = sink ? sink[h] : -CUDART_INF_F;
+    float top = sk;
+    for (int w = 0; w < kLatentWarps; ++w) top = fmaxf(top, part[(size_t)w * (R + 2) + R]);
+    float den = sink ? expf(sk - top) : 0.f;
+    for (int w = 0; w < kLatentWarps; ++w) {
+        const float mw = part[(size_t)w * (R + 2) + R];
+        if (mw != -CUDART_INF_F) den = fmaf(part[(size_t)w * (R + 2) + R + 1], expf(mw - top), den);
+    }
+    const float f = den > 0.f ? 1.0f / den : 0.f;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float o = 0.f;
+        for (int w = 0; w < kLatentWarps; ++w) {
+            const float mw = part[(size_t)w * (R + 2) + R];
+            if (mw != -CUDART_INF_F) o = fmaf(part[(size_t)w * (R + 2) + c], expf(mw - top), o);
+        }
+        out[((size_t)r * H + h) * R + c] = o * f;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -424,6 +492,20 @@ cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c
                                int M, cudaStream_t st) {
     return launch_pdl(latent_prep_kernel, dim3(M), dim3(256), 0, st, proj, ld, q_off, q_rank, c_off, kv_rank, qw, cw, eps,
                       reinterpret_cast<__nv_bfloat16*>(cq_bf16), pages, pm.table, pm.max_pages, pm.page_size, rm.slot, rm.pos);
+}
+
+bool latent_attention_rows_supported(int H, int R) { return H > 0 && H <= 65535 && R > 0 && R <= 32 * kLatentPerLane; }
+
+cudaError_t launch_latent_attention_rows(const float* q, const float* pages, const PageMap& pm, int H, int R, const float* sink,
+                                         const RowMeta& rm, float* out, int M, cudaStream_t st) {
+    if (!latent_attention_rows_supported(H, R)) return cudaErrorNotSupported;
+    const size_t smem = ((size_t)R + (size_t)kLatentWarps * (R + 2)) * 4;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_pdl(latent_attention_rows_kernel, dim3(M, H), dim3(kLatentWarps * 32), smem, st, q, pages, pm.table, pm.max_pages,
+                      pm.page_size, H, R, sink, rm.slot, rm.pos, out);
 }
 
 cudaError_t launch_head_linear(const float* A, int lda, const void* W, float* Y, int ldy, void* y_bf16, int M, int H, int N, int K,

@@ -156,8 +156,11 @@ def test_router_takes_the_largest_biased_logits_and_weighs_outputs_by_their_soft
 
 
 @pytest.mark.parametrize("heads,dim,vdim,q_rank,kv_rank", [(12, 128, 32, 64, 128), (16, 16, 128, 24, 64), (3, 136, 200, 9, 256),
-                                                           (2, 8, 8, 200, 4), (32, 40, 8, 16, 48)])
+                                                           (2, 8, 8, 200, 4), (32, 40, 8, 16, 48), (2, 16, 24, 32, 300), (3, 8, 8, 8, 1000),
+                                                           (130, 8, 4, 16, 20), (40, 12, 8, 16, 250)])
 def test_latent_attention_with_other_shapes(heads, dim, vdim, q_rank, kv_rank):
+    """Tile heights from 16 rows down, latents up to 256 wide on the tiled kernel; wider latents and more heads than a tile
+    holds on the kernel that takes every (row, head) on its own."""
     mixer = {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": dim ** -0.5}
     cfg = small_config(layers=[layer("latent_attention", mixer, None)])
     model, w = build(cfg, 48)
