@@ -50,18 +50,20 @@ __global__ void streams_embed_kernel(const __nv_bfloat16* __restrict__ table, co
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One CTA per (output) row.  X [M][streams][D].  VW = 4: D is a multiple of 4 and every row is moved in 16-byte pieces.
-template <int VW>
+// One CTA per (output) row.  X [M][S][D].  VW = 4: D is a multiple of 4 and every row is moved in 16-byte pieces.  The
+// number of streams is a template argument, so that the old and new values of a column are exactly S registers each.
+template <int VW, int S>
 __global__ void __launch_bounds__(256)
-streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict__ mix, const float* __restrict__ out,
+streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const float* __restrict__ out,
                     const float* __restrict__ y, const float* __restrict__ parts, const int* __restrict__ slot_of,
                     const float* __restrict__ sel_w, int top, const float* __restrict__ in, const float* __restrict__ norm_w,
                     float eps, const int* __restrict__ rows, float* __restrict__ h, __nv_bfloat16* __restrict__ h_b, int D) {
     extern __shared__ __align__(16) float u_s[];              // [D]
     __shared__ float red[32];
-    __shared__ float mix_s[kMaxStreams * kMaxStreams], out_s[kMaxStreams], in_s[kMaxStreams];
+    __shared__ float mix_s[S * S], out_s[S], in_s[S];
     pdl_release();
-    const int tid = threadIdx.x, s = streams;
+    constexpr int s = S;
+    const int tid = threadIdx.x;
     const bool write = (mix != nullptr) && !rows;
     if (tid < s * s) mix_s[tid] = write ? mix[tid] : 0.f;
     if (tid < s) {
@@ -86,9 +88,9 @@ streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict_
     };
     float sum = 0.f;
     for (int c = tid * VW; c < D; c += blockDim.x * VW) {
-        float xs[kMaxStreams][VW];
+        float xs[S][VW];
 #pragma unroll
-        for (int j = 0; j < kMaxStreams; ++j) {
+        for (int j = 0; j < S; ++j) {
             if (j < s) load(xr + (size_t)j * D + c, xs[j]);
             else
 #pragma unroll
@@ -107,14 +109,14 @@ streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict_
 #pragma unroll
                     for (int e = 0; e < VW; ++e) yv[e] = fmaf(wt, pv[e], yv[e]);
                 }
-            float nx[kMaxStreams][VW];
+            float nx[S][VW];
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j) {
+            for (int j = 0; j < S; ++j) {
 #pragma unroll
                 for (int e = 0; e < VW; ++e) nx[j][e] = 0.f;
                 if (j < s) {
 #pragma unroll
-                    for (int i = 0; i < kMaxStreams; ++i)
+                    for (int i = 0; i < S; ++i)
                         if (i < s) {
                             const float mw = mix_s[i * s + j];
 #pragma unroll
@@ -126,7 +128,7 @@ streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict_
                 }
             }
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j)
+            for (int j = 0; j < S; ++j)
 #pragma unroll
                 for (int e = 0; e < VW; ++e) xs[j][e] = nx[j][e];
         }
@@ -135,7 +137,7 @@ streams_step_kernel(float* __restrict__ X, int streams, const float* __restrict_
 #pragma unroll
             for (int e = 0; e < VW; ++e) uv[e] = 0.f;
 #pragma unroll
-            for (int j = 0; j < kMaxStreams; ++j)
+            for (int j = 0; j < S; ++j)
                 if (j < s)
 #pragma unroll
                     for (int e = 0; e < VW; ++e) uv[e] = fmaf(in_s[j], xs[j][e], uv[e]);
@@ -471,7 +473,15 @@ cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, co
     const size_t smem = (size_t)D * 4;
     auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     const bool vec = D % 4 == 0 && aligned(X) && aligned(wr.y) && aligned(wr.parts);
-    auto kernel = vec ? streams_step_kernel<4> : streams_step_kernel<1>;
+    using Kernel = void (*)(float*, const float*, const float*, const float*, const float*, const int*, const float*, int, const float*,
+                            const float*, float, const int*, float*, __nv_bfloat16*, int);
+    Kernel kernel = nullptr;
+    switch (streams) {
+#define STREAMS_CASE(S) case S: kernel = vec ? streams_step_kernel<4, S> : streams_step_kernel<1, S>; break
+        STREAMS_CASE(1); STREAMS_CASE(2); STREAMS_CASE(3); STREAMS_CASE(4);
+        STREAMS_CASE(5); STREAMS_CASE(6); STREAMS_CASE(7); STREAMS_CASE(8);
+#undef STREAMS_CASE
+    }
     static size_t allowed[2][64] = {};
     if (smem > 48 * 1024) {
         int dev = 0;
@@ -483,7 +493,7 @@ cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, co
             if (dev >= 0 && dev < 64) allowed[vec][dev] = smem;
         }
     }
-    return launch_pdl(kernel, dim3(M), dim3(256), smem, st, X, streams, wr.mix, wr.out, wr.y, wr.parts, wr.slot_of, wr.sel_w, wr.top,
+    return launch_pdl(kernel, dim3(M), dim3(256), smem, st, X, wr.mix, wr.out, wr.y, wr.parts, wr.slot_of, wr.sel_w, wr.top,
                       in, norm_w, eps, rows, h, reinterpret_cast<__nv_bfloat16*>(h_bf16), D);
 }
 
