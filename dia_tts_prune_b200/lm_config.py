@@ -262,19 +262,20 @@ class LuketarConfig(BaseModel, frozen=True):
         return cls.model_validate(json.loads(Path(path).read_text(encoding="utf-8")))
 
     def weight_layer(self, i: int) -> int:
-        """The layer whose tensors layer ``i`` uses."""
-        j = self.layers[i].weights_of
-        return i if j is None else j
+        """The layer whose tensors layer ``i`` uses (a named layer that itself names another one is followed)."""
+        seen = {i}
+        while self.layers[i].weights_of is not None:
+            i = self.layers[i].weights_of
+            if i in seen or i >= len(self.layers):
+                raise ValueError("weights_of must lead to a layer that has weights of its own")
+            seen.add(i)
+        return i
 
     def check(self) -> None:
         for i, layer in enumerate(self.layers):
-            j = layer.weights_of
-            if j is not None:
-                if j >= len(self.layers) or j == i or self.layers[j].weights_of is not None:
-                    raise ValueError(f"layer {i}: weights_of ({j}) must name another layer that has weights of its own")
-                other = self.layers[j]
-                if (other.type, other.mixer, other.mlp) != (layer.type, layer.mixer, layer.mlp):
-                    raise ValueError(f"layer {i}: its entry differs from layer {j}, whose weights it uses")
+            j = self.weight_layer(i)
+            if j != i and self.layers[j].type != layer.type:     # (the sizes and constants that run are layer j's)
+                raise ValueError(f"layer {i}: its type differs from layer {j}, whose weights it uses")
             f = layer.mlp
             if f is not None and f.kind == "moe" and f.router.top > f.router.experts:
                 raise ValueError(f"layer {i}: top ({f.router.top}) exceeds experts ({f.router.experts})")

@@ -37,13 +37,18 @@ def test_configuration_is_read_by_layer_type_and_checked():
     p = load_config(plain)
     assert p.streams is None and p.embedding.scale == 1.0
     bad = config()
-    bad["layers"][2]["mixer"]["kv_rank"] = 8                     # differs from the layer whose weights it uses
+    bad["layers"][2]["type"], bad["layers"][2]["mixer"] = "mlstm", bad["layers"][0]["mixer"]     # another kind than the layer whose weights it uses
     with pytest.raises(ValueError):
         load_config(bad).check()
     bad = config()
     bad["layers"][2]["weights_of"] = 2
     with pytest.raises(ValueError):
         load_config(bad).check()
+    chain = config()
+    chain["layers"].append(dict(copy.deepcopy(chain["layers"][2]), weights_of=2))     # names a layer that names layer 1
+    c = load_config(chain)
+    c.check()
+    assert c.weight_layer(4) == 1
     bad = config()
     bad["layers"][1]["mlp"]["router"]["top"] = 6
     with pytest.raises(ValueError):
