@@ -12,12 +12,15 @@ from pathlib import Path
 from . import build as _build
 
 MIXER_SINK_ATTENTION, MIXER_TALK_ATTENTION, MIXER_HGRN2, MIXER_CHANNEL_DELTA, MIXER_LATENT_ATTENTION, MIXER_MLSTM = 1, 2, 3, 4, 5, 6
+MIXER_GATED_DELTA, MIXER_RETENTION = 7, 8
 FF_NONE, FF_ROUTED_EXPERTS, FF_DENSE = 0, 1, 2
-NORM_DYT, NORM_LAYER = 0, 1
+NORM_DYT, NORM_LAYER, NORM_RMS = 0, 1, 2
 FORM_SEQUENTIAL, FORM_PARALLEL, FORM_STREAMS = 0, 1, 2
-ACT_SILU_GLU, ACT_XIELU, ACT_CLAMPED_GLU = 0, 1, 2
-ROUTER_SIGMOID_INPUT, ROUTER_SOFTMAX_TOP = 0, 1
-ABI_VERSION = 3
+ACT_SILU_GLU, ACT_XIELU, ACT_CLAMPED_GLU, ACT_RELU2 = 0, 1, 2, 3
+ROUTER_SIGMOID_INPUT, ROUTER_SOFTMAX_TOP, ROUTER_SOFTMAX_GROUPED = 0, 1, 2
+GATE_SIGMOID, GATE_NONE, GATE_SILU = 0, 1, 2
+ROT_INTERLEAVED, ROT_HALF = 0, 1
+ABI_VERSION = 4
 PRECISION_FP32, PRECISION_BF16 = 0, 1
 E_OK, E_INVAL, E_CUDA, E_NOMEM, E_UNSUPPORTED = 0, -1, -2, -3, -5
 
@@ -44,13 +47,18 @@ class Layer(C.Structure):
                 # the stream form
                 ("streams", _i), ("hc_in", _vp * 2), ("hc_out", _vp * 2), ("hc_mix", _vp * 2), ("q_rank", _i), ("kv_rank", _i),
                 ("q_lat_norm", _vp), ("kv_lat_norm", _vp), ("w_uq", _vp), ("w_uk_t", _vp), ("w_uv", _vp), ("latent_pages", _vp),
-                ("gate_cap", _f), ("rec_aux", _vp), ("router", _i), ("router_bias", _vp), ("act_limit", _f), ("shared_limit", _f)]
+                ("gate_cap", _f), ("rec_aux", _vp), ("router", _i), ("router_bias", _vp), ("act_limit", _f), ("shared_limit", _f),
+                # further mechanisms of the stream form
+                ("parallel", _i), ("mixer_gate", _i), ("rot_layout", _i), ("rot_dim", _i), ("head_decay", _vp),
+                ("identity_experts", _i), ("group_count", _i), ("group_keep", _i), ("route_scale", _f), ("route_correction", _vp),
+                ("shared_gate", _i)]
 
 
 class Model(C.Structure):
     _fields_ = [("n_layer", _i), ("width", _i), ("vocab", _i), ("taps", _i), ("page_size", _i), ("max_pages", _i),
                 ("n_slots", _i), ("max_rows", _i), ("eps", _f), ("precision", _i), ("embed", _vp), ("head", _vp),
-                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("logit_scale", _f), ("embed_scale", _f)]
+                ("final_norm", Norm), ("page_table", _vp), ("step_graphs", _i), ("logit_scale", _f), ("embed_scale", _f),
+                ("embed_norm", _vp)]
 
 
 _ci = C.c_int

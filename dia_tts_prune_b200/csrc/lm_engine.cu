@@ -118,6 +118,9 @@ struct lm_b200_engine {
     // space, attended latents / raw read-outs, normaliser floors, and two constants {0, 1}
     float *xs, *qlat, *olat, *floorb, *unit;
     void* cqb;
+    // records whose sublayers read the same streams: the mixer's output beside the feed-forward's, and the feed-forward's input
+    float *ymix, *h2;
+    void* h2b;
     bool stream_form = false;
     float* split_ws;                             // partial results of the key splits of a few rows' attention
     unsigned* split_arrived;                     // ... and their arrival counters (zero between launches)
@@ -218,53 +221,96 @@ int check_parallel_layer(const lm_b200_model& m, const lm_b200_layer& l) {
     (void)m;
 }
 
-// columns of the stacked projections of a stream record
-struct StreamCols { int q, k, v, ig, fg, gate, lat_q, lat_c, n; };
+// columns of the stacked projections of a stream record (gate < 0: the mixer has no gate columns)
+struct StreamCols { int q, k, v, ig, fg, gate, lat_q, lat_c, beta, a, n; };
 StreamCols stream_cols(const lm_b200_layer& l) {
     StreamCols c{};
-    const int H = l.heads, d = l.dim, dv = l.vdim;
+    const int H = l.heads, G = l.kv_heads, d = l.dim, dv = l.vdim;
     int at = 0;
     if (l.mixer == LM_B200_MIXER_LATENT_ATTENTION) {
-        c.lat_q = at; at += l.q_rank; c.lat_c = at; at += l.kv_rank;
+        c.lat_q = at; at += l.q_rank; c.lat_c = at; at += l.kv_rank + l.rot_dim;   // the latent, then the turned key part
+    } else if (l.mixer == LM_B200_MIXER_GATED_DELTA) {
+        c.q = at; at += G * d; c.k = at; at += G * d; c.v = at; at += H * dv; c.beta = at; at += H; c.a = at; at += H;
+    } else if (l.mixer == LM_B200_MIXER_RETENTION) {
+        c.q = at; at += H * d; c.k = at; at += H * d; c.v = at; at += H * dv;
     } else {
         c.q = at; at += H * d; c.k = at; at += H * d; c.v = at; at += H * dv; c.ig = at; at += H; c.fg = at; at += H;
     }
-    c.gate = at; at += H * dv;
+    c.gate = -1;
+    if (l.mixer_gate != LM_B200_GATE_NONE) { c.gate = at; at += H * dv; }
     c.n = (at + 3) & ~3;
     return c;
 }
+// the attention over the cached rows [latent | turned key part]: all of a row is the key, its first kv_rank channels the value
 lm::TalkShape latent_shape(const lm_b200_layer& l) {
-    return lm::TalkShape{l.heads, 1, l.kv_rank, l.kv_rank, 0, 1.f, nullptr, nullptr, l.sink};
+    return lm::TalkShape{l.heads, 1, l.kv_rank + l.rot_dim, l.kv_rank, 0, 1.f, nullptr, nullptr, l.sink, l.window > 0 ? l.window : 0};
 }
+// row of the recurrence inputs of a gated delta record: q | k | v | decay | beta
+int delta_rec_cols(const lm_b200_layer& l) {
+    return l.mixer == LM_B200_MIXER_GATED_DELTA ? 2 * l.kv_heads * l.dim + l.heads * l.vdim + 2 * l.heads : 0;
+}
+bool stream_norm_ok(const lm_b200_norm& n) { return n.w && (n.kind == LM_B200_NORM_LAYER || n.kind == LM_B200_NORM_RMS); }
+// router outputs of a record and the columns of its logits (the shared unit's gate row behind them)
+int route_outputs(const lm_b200_layer& l) { return l.experts + (l.router == LM_B200_ROUTER_SOFTMAX_GROUPED ? l.identity_experts : 0); }
+int route_cols(const lm_b200_layer& l) { return route_outputs(l) + (l.router == LM_B200_ROUTER_SOFTMAX_GROUPED && l.shared_gate ? 1 : 0); }
 
 int check_stream_layer(const lm_b200_model& m, const lm_b200_layer& l) {
     if (l.streams < 1 || l.streams > 8) return LM_B200_EUNSUPPORTED;
-    if (l.norm_mix_in.kind != LM_B200_NORM_LAYER || !l.norm_mix_in.w) return LM_B200_EINVAL;
+    if (!stream_norm_ok(l.norm_mix_in)) return LM_B200_EINVAL;
     if (l.heads <= 0 || l.dim <= 0 || l.vdim <= 0 || !l.w_in || !l.w_o || l.n_in != stream_cols(l).n) return LM_B200_EINVAL;
+    if (l.mixer_gate != LM_B200_GATE_SIGMOID && l.mixer_gate != LM_B200_GATE_NONE && l.mixer_gate != LM_B200_GATE_SILU)
+        return LM_B200_EINVAL;
     for (int q = 0; q < (l.ff == LM_B200_FF_NONE ? 1 : 2); ++q)
         if (!l.hc_in[q] || !l.hc_out[q] || !l.hc_mix[q]) return LM_B200_EINVAL;
+    const bool rot_ok = l.rot_dims >= 0 && l.rot_dims % 2 == 0 && (l.rot_dims == 0 || l.rot_freq) &&
+                        (l.rot_layout == LM_B200_ROT_INTERLEAVED || l.rot_layout == LM_B200_ROT_HALF);
     switch (l.mixer) {
         case LM_B200_MIXER_LATENT_ATTENTION:
             if (l.q_rank <= 0 || l.kv_rank <= 0 || !l.q_lat_norm || !l.kv_lat_norm || !l.w_uq || !l.w_uk_t || !l.w_uv ||
-                !l.latent_pages)
+                !l.latent_pages || l.rot_dim < 0 || !rot_ok || l.rot_dims > l.rot_dim)
                 return LM_B200_EINVAL;
-            if (!lm::talk_attention_supported(latent_shape(l)) && !lm::latent_attention_rows_supported(l.heads, l.kv_rank))
+            if (l.mixer_gate == LM_B200_GATE_SILU) return LM_B200_EUNSUPPORTED;
+            if (!lm::talk_attention_supported(latent_shape(l)) && !lm::latent_attention_rows_supported(l.heads, l.kv_rank + l.rot_dim))
                 return LM_B200_EUNSUPPORTED;
             break;
         case LM_B200_MIXER_MLSTM:
-            if (!l.head_norm || !l.rec_state || !l.rec_aux || !(l.gate_cap > 0.f)) return LM_B200_EINVAL;
+            if (!l.head_norm || !l.rec_state || !l.rec_aux || !(l.gate_cap > 0.f) || l.mixer_gate != LM_B200_GATE_SIGMOID)
+                return LM_B200_EINVAL;
             if (l.dim > 256 || l.heads > 65535) return LM_B200_EUNSUPPORTED;
+            break;
+        case LM_B200_MIXER_GATED_DELTA:
+            if (l.kv_heads <= 0 || l.heads % l.kv_heads || !l.head_norm || !l.rec_state || !l.conv_w || !l.a_log || !l.dt_bias ||
+                l.conv_taps < 1 || (l.conv_taps > 1 && !l.conv_tail))
+                return LM_B200_EINVAL;
+            if (l.dim > 256 || l.heads > 65535 || l.conv_taps > lm::kMaxTaps) return LM_B200_EUNSUPPORTED;
+            break;
+        case LM_B200_MIXER_RETENTION:
+            if (!l.rec_state || !l.head_decay || !rot_ok || l.rot_dims > l.dim) return LM_B200_EINVAL;
+            if (l.dim > 256 || l.heads > 32767) return LM_B200_EUNSUPPORTED;
             break;
         default: return LM_B200_EUNSUPPORTED;
     }
     if (l.ff == LM_B200_FF_NONE) return LM_B200_OK;
-    if (!l.norm_ff_in.w || l.norm_ff_in.kind != LM_B200_NORM_LAYER) return LM_B200_EINVAL;
+    if (!stream_norm_ok(l.norm_ff_in)) return LM_B200_EINVAL;
+    if (l.parallel && l.norm_ff_in.kind != l.norm_mix_in.kind) return LM_B200_EUNSUPPORTED;
+    if (l.ff == LM_B200_FF_DENSE && l.act == LM_B200_ACT_RELU2) return (l.dense_ff > 0 && l.ws_gate_up && l.ws_down) ? LM_B200_OK : LM_B200_EINVAL;
     if (l.act != LM_B200_ACT_CLAMPED_GLU && l.act != LM_B200_ACT_SILU_GLU) return LM_B200_EUNSUPPORTED;
     if (l.ff == LM_B200_FF_DENSE) return (l.dense_ff > 0 && l.ws_gate_up && l.ws_down) ? LM_B200_OK : LM_B200_EINVAL;
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EUNSUPPORTED;
-    if (l.experts <= 0 || l.top <= 0 || l.top > l.experts || l.expert_ff <= 0 || l.shared_ff < 0) return LM_B200_EINVAL;
+    if (l.experts <= 0 || l.top <= 0 || l.expert_ff <= 0 || l.shared_ff < 0) return LM_B200_EINVAL;
     if (!l.w_router || !l.w_gate_up || !l.w_down || (l.shared_ff > 0 && (!l.ws_gate_up || !l.ws_down))) return LM_B200_EINVAL;
-    if (l.router != LM_B200_ROUTER_SOFTMAX_TOP) return LM_B200_EUNSUPPORTED;
+    if (l.router == LM_B200_ROUTER_SOFTMAX_GROUPED) {
+        const int n = route_outputs(l);
+        if (l.identity_experts < 0 || l.top > n || (l.shared_gate && l.shared_ff <= 0)) return LM_B200_EINVAL;
+        if (l.group_count > 1 && (n % l.group_count || l.group_keep < 1 || l.group_keep > l.group_count ||
+                                  l.top > l.group_keep * (n / l.group_count)))
+            return LM_B200_EINVAL;
+        if ((size_t)(2 * n + 1 + l.group_count) * sizeof(float) > 40000) return LM_B200_EUNSUPPORTED;
+    } else if (l.router != LM_B200_ROUTER_SOFTMAX_TOP) {
+        return LM_B200_EUNSUPPORTED;
+    } else if (l.top > l.experts) {
+        return LM_B200_EINVAL;
+    }
     if (3 * (size_t)l.experts * sizeof(int) > 40000) return LM_B200_EUNSUPPORTED;
     (void)m;
     return LM_B200_OK;
@@ -534,23 +580,48 @@ int stream_mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
     const StreamCols c = stream_cols(l);
     int rc = product_ld(e, h, D, hb, l.w_in, e->proj, M, c.n, D, st);
     if (rc) return rc;
+    const float* gate = c.gate >= 0 ? e->proj + c.gate : nullptr;
+    const int gate_act = l.mixer_gate == LM_B200_GATE_SILU ? 2 : 1;
     if (l.mixer == LM_B200_MIXER_LATENT_ATTENTION) {
         const lm::PageMap pm{e->m.page_table, e->m.max_pages, e->m.page_size};
-        const int nq = H * l.dim, nl = H * l.kv_rank;
+        // a query head is [dim plain | rot_dim turned]; a cached row is [latent | turned key part]
+        const int rd = l.rot_dim, dq = l.dim + rd, RK = l.kv_rank + rd, nq = H * dq, nl = H * RK, no = H * l.kv_rank;
+        const lm::RotPart rot{rd, l.rot_dims, l.rot_layout, l.rot_freq};
         LCK(lm::launch_latent_prep(e->proj, c.n, c.lat_q, l.q_rank, c.lat_c, l.kv_rank, l.q_lat_norm, l.kv_lat_norm, e->m.eps,
-                                   bf ? e->cqb : nullptr, l.latent_pages, pm, v.rm, M, st));
+                                   bf ? e->cqb : nullptr, l.latent_pages, pm, v.rm, M, st, rot));
         rc = product_ld(e, e->proj + c.lat_q, c.n, bf ? e->cqb : nullptr, l.w_uq, e->qk, M, nq, l.q_rank, st);
         if (rc) return rc;
-        // scores q_h . (W_uk,h c_j) = (W_uk,h^T q_h) . c_j: the query goes into the latent space, with the score multiplier
-        LCK(lm::launch_head_linear(e->qk, nq, l.w_uk_t, e->qlat, nl, nullptr, M, H, l.kv_rank, l.dim, l.scale, nullptr, 0, st));
+        // scores q_h . (W_uk,h c_j) = (W_uk,h^T q_h) . c_j: the query goes into the latent space, with the score multiplier;
+        // its turned part stands behind it, against the turned key part of the cached row
+        LCK(lm::launch_head_linear(e->qk, nq, l.w_uk_t, e->qlat, nl, nullptr, M, H, l.kv_rank, l.dim, l.scale, nullptr, 0, st, dq, RK));
+        if (rd > 0)
+            LCK(lm::launch_rot_rows(e->qk, nq, l.dim, dq, e->qlat, nl, l.kv_rank, RK, H, rd, rot, H, l.scale, l.scale, v.rm, M, st));
         if (lm::talk_attention_supported(latent_shape(l)))
-            LCK(lm::launch_talk_attention(e->qlat, nl, 0, -1, l.latent_pages, l.latent_pages, pm, latent_shape(l), v.rm, e->olat, nl,
+            LCK(lm::launch_talk_attention(e->qlat, nl, 0, -1, l.latent_pages, l.latent_pages, pm, latent_shape(l), v.rm, e->olat, no,
                                           nullptr, e->split_ws, e->split_arrived, M, st));
         else
-            LCK(lm::launch_latent_attention_rows(e->qlat, l.latent_pages, pm, H, l.kv_rank, l.sink, v.rm, e->olat, M, st));
+            LCK(lm::launch_latent_attention_rows(e->qlat, l.latent_pages, pm, H, l.kv_rank, l.sink, v.rm, e->olat, M, st, rd,
+                                                 l.window > 0 ? l.window : 0));
         // sum_j p_j (W_uv,h c_j) = W_uv,h (sum_j p_j c_j), times the sigmoid of the gate columns
-        LCK(lm::launch_head_linear(e->olat, nl, l.w_uv, e->att, nv, bf ? e->attb : nullptr, M, H, l.vdim, l.kv_rank, 1.f,
-                                   e->proj + c.gate, c.n, st));
+        LCK(lm::launch_head_linear(e->olat, no, l.w_uv, e->att, nv, bf ? e->attb : nullptr, M, H, l.vdim, l.kv_rank, 1.f, gate, c.n, st));
+    } else if (l.mixer == LM_B200_MIXER_GATED_DELTA) {
+        const lm::DeltaShape d{H, l.kv_heads, l.dim, l.vdim, l.conv_taps, l.unit_eps, l.conv_w, l.a_log, l.dt_bias};
+        const int k0 = l.kv_heads * l.dim, v0 = 2 * k0, d0 = v0 + nv, b0 = d0 + H, ldr = delta_rec_cols(l);
+        LCK(lm::launch_delta_prep(e->proj, c.n, c.beta, d, l.conv_tail, v.rm, e->rec, ldr, M, st, c.a));
+        LCK(lm::launch_conv_tail(e->proj, c.n, v0 + nv, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
+        const lm::ScanInputs si{0, k0, d0, v0, b0};
+        LCK(lm::launch_column_scan(e->rec, ldr, si, true, H, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq, e->att, nv, st,
+                                   true));
+        LCK(lm::launch_head_norm_gate(e->att, nv, bf ? e->attb : nullptr, l.head_norm, gate, c.n, H, l.vdim, e->m.eps, M, st, gate_act));
+    } else if (l.mixer == LM_B200_MIXER_RETENTION) {
+        // q and k (adjacent in the row) turn in place, k also takes dim^-1/2; decay fixed per head, no write gate, no normaliser
+        const lm::RotPart rot{l.dim, l.rot_dims, l.rot_layout, l.rot_freq};
+        LCK(lm::launch_rot_rows(e->proj, c.n, c.q, l.dim, e->proj, c.n, c.q, l.dim, 2 * H, l.dim, rot, H, 1.f,
+                                1.0f / sqrtf((float)l.dim), v.rm, M, st));
+        const lm::ScanInputs si{c.q, c.k, 0, c.v, 0};
+        LCK(lm::launch_scalar_gate_scan(e->proj, c.n, si, H, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq, e->att, nv, st,
+                                        l.head_decay, false));
+        LCK(lm::launch_head_norm_gate(e->att, nv, bf ? e->attb : nullptr, l.head_norm, gate, c.n, H, l.vdim, e->m.eps, M, st, gate_act));
     } else {
         LCK(lm::launch_mlstm_gates(e->proj, c.n, c.ig, c.fg, l.in_bias, l.gate_cap, H, l.rec_aux, v.sm, v.rm, n_seq, e->floorb, st));
         const lm::ScanInputs si{c.q, c.k, c.fg, c.v, c.ig};      // decay in the forget column, write strength in the input column
@@ -560,6 +631,22 @@ int stream_mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
                                     c.n, e->m.eps, e->att, bf ? e->attb : nullptr, M, H, l.vdim, st));
     }
     return product_ld(e, e->att, nv, bf ? e->attb : nullptr, l.w_o, y, M, D, nv, st);
+}
+
+// a dense unit that is not gated: out = max(h W_up^T, 0)^2 W_down^T
+int relu2_unit(lm_b200_engine* e, const float* h, const void* hb, int M, const void* w_up, const void* w_down, int F, float* out,
+               cudaStream_t st) {
+    const int D = e->m.width;
+    if (hb && tensor_path(e, M, F, D) && tensor_path(e, M, D, F)) {
+        LCK(dia::launch_gemm_tcgen05_bf16(hb, 1, w_up, F, e->sgu, M, F, D, kPlain, nullptr, st));
+        LCK(lm::launch_xielu_rows(e->sgu, F, 0, 0.f, 0.f, nullptr, F, 0, e->smidb, M, F, st, true));
+        LCK(dia::launch_gemm_tcgen05_bf16(e->smidb, 1, w_down, D, out, M, D, F, kPlain, nullptr, st));
+        return LM_B200_OK;
+    }
+    LCK(lm::launch_linear(h, D, w_up, 0, e->sgu, F, M, F, D, nullptr, st));
+    LCK(lm::launch_xielu_rows(e->sgu, F, 0, 0.f, 0.f, e->smid, F, 0, nullptr, M, F, st, true));
+    LCK(lm::launch_linear(e->smid, F, w_down, 0, out, D, M, D, F, nullptr, st));
+    return LM_B200_OK;
 }
 
 // one gated unit on all rows: out = act([gate | up] h) W_down^T
@@ -584,26 +671,35 @@ int gated_unit(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const 
 }
 
 // the feed-forward of a stream record: fills what the following streams_step adds (wr->y and, for grouped experts, the
-// expert outputs with their weights)
+// expert outputs with their weights; wx: the input rows identity experts return, the shared unit's gate)
 int stream_ff(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const void* hb, int M, lm::StreamWrite* wr,
-              cudaStream_t st) {
+              lm::StreamExtra* wx, cudaStream_t st) {
     const int D = e->m.width, E = l.experts, top = l.top, F = l.expert_ff, Sf = l.shared_ff;
     const int act = l.act == LM_B200_ACT_CLAMPED_GLU ? 1 : 0;
     wr->y = e->y; wr->parts = nullptr; wr->slot_of = nullptr; wr->sel_w = nullptr; wr->top = 0;
-    if (l.ff == LM_B200_FF_DENSE) return gated_unit(e, l, h, hb, M, l.ws_gate_up, l.ws_down, l.dense_ff, l.act_limit, e->y, st);
+    if (l.ff == LM_B200_FF_DENSE) {
+        if (l.act == LM_B200_ACT_RELU2) return relu2_unit(e, h, hb, M, l.ws_gate_up, l.ws_down, l.dense_ff, e->y, st);
+        return gated_unit(e, l, h, hb, M, l.ws_gate_up, l.ws_down, l.dense_ff, l.act_limit, e->y, st);
+    }
+    const bool grouped = l.router == LM_B200_ROUTER_SOFTMAX_GROUPED;
+    const int Et = route_outputs(l), zc = route_cols(l);         // router outputs; columns of the logits (+ the shared unit's gate)
+    const lm::GroupedRoute gr{Et, E, l.group_count, l.group_keep, l.route_scale, l.route_correction};
+    const float* sgate = (grouped && l.shared_gate) ? e->z + Et : nullptr;
     if (M <= lm::kRowsKernelMax) {
         const lm::GroupMap rows{e->a_row, e->a_scale, e->a_expert, e->n_slots};
-        LCK(lm::launch_router_rows(h, D, l.w_router, E, top, M, e->z, rows, e->slot_of, st, l.router_bias, true));
+        LCK(lm::launch_router_rows(h, D, l.w_router, zc, top, M, e->z, rows, e->slot_of, st, l.router_bias, !grouped,
+                                   grouped ? &gr : nullptr));
         const lm::GroupMap unscaled{e->a_row, nullptr, e->a_expert, e->n_slots};    // the weight is for the expert's OUTPUT
         const lm::GluAct ga{act, l.act_limit, l.shared_limit};
         LCK(lm::launch_gated_rows(h, D, l.w_gate_up, 2LL * F * D, e->mid, M * top, F, D, &unscaled, l.ws_gate_up, e->smid,
                                   Sf > 0 ? M : 0, Sf, st, ga));
         LCK(lm::launch_down_combine_rows(e->mid, F, l.w_down, e->a_expert, top, Sf > 0 ? e->smid : nullptr, Sf, l.ws_down, e->y, M, D,
-                                         lm::NormW{nullptr, nullptr, 0.f}, lm::TapOut{}, st, e->a_scale));
+                                         lm::NormW{nullptr, nullptr, 0.f}, lm::TapOut{}, st, e->a_scale, grouped ? E : 0,
+                                         grouped ? h : nullptr, sgate, zc));
         return LM_B200_OK;
     }
-    LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, E, M, E, D, nullptr, st));
-    LCK(lm::launch_router_topk(e->z, E, top, M, e->sel_e, e->sel_w, st, l.router_bias, true));
+    LCK(lm::launch_linear(h, D, l.w_router, 0, e->z, zc, M, zc, D, nullptr, st));
+    LCK(lm::launch_router_topk(e->z, zc, top, M, e->sel_e, e->sel_w, st, l.router_bias, !grouped, grouped ? &gr : nullptr));
     const bool tc = hb && tensor_path(e, M, 2 * F, D) && tensor_path(e, M, D, F);
     const int pad = tc ? dia::kGemmRowTile : lm::kTileRows;
     const int bound = slots_bound(M, top, E, pad);
@@ -628,8 +724,11 @@ int stream_ff(lm_b200_engine* e, const lm_b200_layer& l, const float* h, const v
         const int rc = gated_unit(e, l, h, hb, M, l.ws_gate_up, l.ws_down, Sf, l.shared_limit, e->y, st);
         if (rc) return rc;
         wr->y = e->y;
+        wx->y_gate = sgate;
+        wx->y_gate_ld = zc;
     }
     wr->parts = e->parts; wr->slot_of = e->slot_of; wr->sel_w = e->sel_w; wr->top = top;
+    if (grouped) wx->ident_h = h;
     return LM_B200_OK;
 }
 
@@ -647,7 +746,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     if (m.n_layer <= 0 || m.width <= 0 || m.vocab <= 0 || m.taps < 0 || m.taps > lm::kMaxTaps || m.page_size <= 0 ||
         m.max_pages <= 0 || m.n_slots <= 0 || m.max_rows <= 0 ||
         (m.precision != LM_B200_PRECISION_FP32 && m.precision != LM_B200_PRECISION_BF16) || !m.embed || !m.head || !m.final_norm.w ||
-        (!m.final_norm.b && m.final_norm.kind != LM_B200_NORM_LAYER) || !m.page_table)
+        (!m.final_norm.b && m.final_norm.kind != LM_B200_NORM_LAYER && m.final_norm.kind != LM_B200_NORM_RMS) || !m.page_table)
         return LM_B200_EINVAL;
     for (int i = 0; i < m.n_layer; ++i) {
         const int rc = check_layer(m, layers[i]);
@@ -667,7 +766,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     size_t qk = 0, att = 0, E = 1, top = 1, F = 1, Sf = 1, slots = 1;
     size_t n_in = 0, k_out = 0, n_rec = 0, split_dim = 0;
     size_t n_streams = 0, n_lat = 0, q_rank = 0, n_heads = 0;
-    bool pre = false;
+    bool pre = false, any_parallel = false;
     e->stream_form = e->layers[0].form == LM_B200_FORM_STREAMS;
     for (const lm_b200_layer& l : e->layers) {
         if (l.form == LM_B200_FORM_STREAMS) {
@@ -676,16 +775,18 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
             att = std::max(att, (size_t)l.heads * l.vdim);
             n_heads = std::max(n_heads, (size_t)l.heads);
             if (l.mixer == LM_B200_MIXER_LATENT_ATTENTION) {
-                qk = std::max(qk, (size_t)l.heads * l.dim);
-                n_lat = std::max(n_lat, (size_t)l.heads * l.kv_rank);
+                qk = std::max(qk, (size_t)l.heads * (l.dim + l.rot_dim));
+                n_lat = std::max(n_lat, (size_t)l.heads * (l.kv_rank + l.rot_dim));
                 q_rank = std::max(q_rank, (size_t)l.q_rank);
                 if (lm::talk_attention_supported(latent_shape(l))) split_dim = std::max(split_dim, (size_t)l.heads * (l.kv_rank + 2));
-            } else {
+            } else if (l.mixer == LM_B200_MIXER_MLSTM) {
                 n_lat = std::max(n_lat, (size_t)l.heads * (l.vdim + 1));
             }
+            n_rec = std::max(n_rec, (size_t)delta_rec_cols(l));
+            any_parallel = any_parallel || (l.parallel && l.ff != LM_B200_FF_NONE);
             if (l.ff == LM_B200_FF_DENSE) Sf = std::max(Sf, (size_t)l.dense_ff);
             if (l.ff == LM_B200_FF_ROUTED_EXPERTS) {
-                E = std::max(E, (size_t)l.experts);
+                E = std::max(E, (size_t)route_cols(l));
                 top = std::max(top, (size_t)l.top);
                 F = std::max(F, (size_t)l.expert_ff);
                 Sf = std::max(Sf, (size_t)l.shared_ff);
@@ -724,6 +825,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
                  o_rec = take(R * n_rec * 4), o_outcat = take(R * k_out * 4);
     const size_t o_xs = take(R * n_streams * D * 4), o_qlat = take(R * n_lat * 4), o_olat = take(R * n_lat * 4),
                  o_floor = take(R * n_heads * 4), o_unit = take(2 * 4);
+    const size_t o_ymix = take(any_parallel ? R * D * 4 : 0), o_h2 = take(any_parallel ? R * D * 4 : 0);
     const size_t o_split = take((size_t)lm::kAttnRowsKernelMax * lm::kAttnSplitsMax * split_dim * 4);
     size_t max_heads = 1;
     for (const lm_b200_layer& l : e->layers) max_heads = std::max(max_heads, (size_t)l.heads);
@@ -733,7 +835,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     const size_t o_hb = take(tcb ? R * D * 2 : 0), o_attb = take(tcb ? R * att * 2 : 0), o_packb = take(tcb ? slots * D * 2 : 0),
                  o_midb = take(tcb ? slots * F * 2 : 0), o_smidb = take(tcb ? R * Sf * 2 : 0), o_hwb = take(tcb ? R * D * 2 : 0);
     const size_t o_catb = take(tcb && pre ? R * 2 * D * 2 : 0), o_outcatb = take(tcb ? R * k_out * 2 : 0);
-    const size_t o_cqb = take(tcb ? R * q_rank * 2 : 0);
+    const size_t o_cqb = take(tcb ? R * q_rank * 2 : 0), o_h2b = take(tcb && any_parallel ? R * D * 2 : 0);
     if (cudaMalloc(&e->arena, off) != cudaSuccess) {
         (void)cudaGetLastError();
         delete e;
@@ -753,6 +855,7 @@ int lm_b200_engine_create(const lm_b200_model* model, const lm_b200_layer* layer
     e->outcat = (float*)(b + o_outcat); e->catb = b + o_catb; e->outcatb = b + o_outcatb;
     e->xs = (float*)(b + o_xs); e->qlat = (float*)(b + o_qlat); e->olat = (float*)(b + o_olat); e->floorb = (float*)(b + o_floor);
     e->unit = (float*)(b + o_unit); e->cqb = b + o_cqb;
+    e->ymix = (float*)(b + o_ymix); e->h2 = (float*)(b + o_h2); e->h2b = b + o_h2b;
     e->split_ws = (float*)(b + o_split);
     e->split_arrived = (unsigned*)(b + o_arrived);
     const float unit_host[2] = {0.f, 1.f};
@@ -793,9 +896,10 @@ int head_rows(lm_b200_engine* e, const StepView& v, int n_want, float* logits_ou
         // sequences) the tensor-core kernel reads it once for all rows, where the row kernel reads it once per row
         const bool tc = e->m.precision == LM_B200_PRECISION_BF16 && n_want >= kHeadTensorRowsMin &&
                         dia::gemm_tcgen05_shape_ok(n_want, e->m.vocab, D) && (reinterpret_cast<uintptr_t>(logits_out) & 15) == 0;
-        if (e->m.final_norm.kind == LM_B200_NORM_LAYER)
+        if (e->m.final_norm.kind == LM_B200_NORM_LAYER || e->m.final_norm.kind == LM_B200_NORM_RMS)
             LCK(lm::launch_layernorm_rows(e->x, v.want, e->m.final_norm.w, e->m.final_norm.b, e->m.eps,
-                                          e->m.logit_scale != 0.f ? e->m.logit_scale : 1.f, e->hw, tc ? e->hwb : nullptr, n_want, D, st));
+                                          e->m.logit_scale != 0.f ? e->m.logit_scale : 1.f, e->hw, tc ? e->hwb : nullptr, n_want, D, st,
+                                          e->m.final_norm.kind == LM_B200_NORM_RMS));
         else
             LCK(lm::launch_dyt_gather(e->x, v.want, N(e->m.final_norm), e->hw, tc ? e->hwb : nullptr, n_want, D, st));
         if (tc)
@@ -813,17 +917,47 @@ int run_stream_layers(lm_b200_engine* e, const StepView& v, int M, int n_seq, fl
     const float eps = e->m.eps;
     const bool bf = e->m.precision == LM_B200_PRECISION_BF16 && M >= kTensorRowsMin;
     void* hb = bf ? e->hb : nullptr;
-    LCK(lm::launch_streams_embed(e->m.embed, v.token, e->m.embed_scale != 0.f ? e->m.embed_scale : 1.f, e->xs, s, M, e->m.vocab, D, st));
+    void* h2b = bf ? e->h2b : nullptr;
+    LCK(lm::launch_streams_embed(e->m.embed, v.token, e->m.embed_scale != 0.f ? e->m.embed_scale : 1.f, e->xs, s, M, e->m.vocab, D, st,
+                                 e->m.embed_norm, eps));
     const lm::StreamWrite none{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0};
-    LCK(lm::launch_streams_step(e->xs, s, none, e->layers[0].hc_in[0], e->layers[0].norm_mix_in.w, eps, nullptr, e->h, hb, M, D, st));
+    // A parallel record's feed-forward reads the streams the mixer read.  With one stream and one set of read weights both
+    // norms share their statistics, and the step that produces the mixer's input writes the feed-forward's beside it.
+    auto shares_read = [&](const lm_b200_layer& l) {
+        return l.parallel && l.ff != LM_B200_FF_NONE && s == 1 && l.hc_in[0] == l.hc_in[1];
+    };
+    auto read_of = [&](const lm_b200_layer& l, lm::StreamExtra ex) {
+        ex.rms = l.norm_mix_in.kind == LM_B200_NORM_RMS;
+        if (shares_read(l)) { ex.norm_w2 = l.norm_ff_in.w; ex.h2 = e->h2; ex.h2_b = h2b; }
+        return ex;
+    };
+    LCK(lm::launch_streams_step(e->xs, s, none, e->layers[0].hc_in[0], e->layers[0].norm_mix_in.w, eps, nullptr, e->h, hb, M, D, st,
+                                read_of(e->layers[0], lm::StreamExtra{})));
     for (int i = 0; i < n; ++i) {
         const lm_b200_layer& l = e->layers[i];
-        int rc = stream_mixer(e, l, e->h, hb, v, M, n_seq, e->y, st);
+        const bool par = l.parallel && l.ff != LM_B200_FF_NONE;
+        int rc = stream_mixer(e, l, e->h, hb, v, M, n_seq, par ? e->ymix : e->y, st);
         if (rc) return rc;
         lm::StreamWrite wr{l.hc_mix[0], l.hc_out[0], e->y, nullptr, nullptr, nullptr, 0};
-        if (l.ff != LM_B200_FF_NONE) {
-            LCK(lm::launch_streams_step(e->xs, s, wr, l.hc_in[1], l.norm_ff_in.w, eps, nullptr, e->h, hb, M, D, st));
-            rc = stream_ff(e, l, e->h, hb, M, &wr, st);
+        lm::StreamExtra wx{};
+        if (par) {
+            if (!shares_read(l)) {
+                lm::StreamExtra rx{};
+                rx.rms = l.norm_ff_in.kind == LM_B200_NORM_RMS;
+                LCK(lm::launch_streams_step(e->xs, s, none, l.hc_in[1], l.norm_ff_in.w, eps, nullptr, e->h2, h2b, M, D, st, rx));
+            }
+            rc = stream_ff(e, l, e->h2, h2b, M, &wr, &wx, st);
+            if (rc) return rc;
+            // one write for both sublayers: the streams mix once, the feed-forward's output goes in with its own write weights
+            // and the mixer's beside it with the mixer's
+            wr.out = l.hc_out[1];
+            wx.y2 = e->ymix;
+            wx.out2 = l.hc_out[0];
+        } else if (l.ff != LM_B200_FF_NONE) {
+            lm::StreamExtra rx{};
+            rx.rms = l.norm_ff_in.kind == LM_B200_NORM_RMS;
+            LCK(lm::launch_streams_step(e->xs, s, wr, l.hc_in[1], l.norm_ff_in.w, eps, nullptr, e->h, hb, M, D, st, rx));
+            rc = stream_ff(e, l, e->h, hb, M, &wr, &wx, st);
             if (rc) return rc;
             wr.mix = l.hc_mix[1];
             wr.out = l.hc_out[1];
@@ -831,11 +965,11 @@ int run_stream_layers(lm_b200_engine* e, const StepView& v, int M, int n_seq, fl
         // this sublayer's write with the next layer's read, or with the closing sum of the streams
         if (i + 1 < n) {
             const lm_b200_layer& nx = e->layers[i + 1];
-            LCK(lm::launch_streams_step(e->xs, s, wr, nx.hc_in[0], nx.norm_mix_in.w, eps, nullptr, e->h, hb, M, D, st));
+            LCK(lm::launch_streams_step(e->xs, s, wr, nx.hc_in[0], nx.norm_mix_in.w, eps, nullptr, e->h, hb, M, D, st, read_of(nx, wx)));
             if (layers_out)
                 LCK(lm::launch_streams_step(e->xs, s, none, nullptr, nullptr, eps, nullptr, layers_out + (size_t)i * M * D, nullptr, M, D, st));
         } else {
-            LCK(lm::launch_streams_step(e->xs, s, wr, nullptr, nullptr, eps, nullptr, e->x, nullptr, M, D, st));
+            LCK(lm::launch_streams_step(e->xs, s, wr, nullptr, nullptr, eps, nullptr, e->x, nullptr, M, D, st, wx));
             if (layers_out && cudaMemcpyAsync(layers_out + (size_t)i * M * D, e->x, (size_t)M * D * 4, cudaMemcpyDeviceToDevice, st) !=
                                   cudaSuccess)
                 return cuda_fail(cudaGetLastError());
@@ -1038,13 +1172,14 @@ int lm_b200_op_ff(lm_b200_engine* e, int layer, const float* h, int M, float* y,
             hb = e->hb;
         }
         lm::StreamWrite wr{};
-        const int rc = stream_ff(e, l, h, hb, M, &wr, S(stream));
+        lm::StreamExtra wx{};
+        const int rc = stream_ff(e, l, h, hb, M, &wr, &wx, S(stream));
         if (rc) return rc;
         // y = 0 * y + 1 * (the unit's output + the weighted expert outputs): one stream, mix {0}, out {1}
         if (cudaMemsetAsync(y, 0, (size_t)M * e->m.width * 4, S(stream)) != cudaSuccess) return cuda_fail(cudaGetLastError());
         wr.mix = e->unit;
         wr.out = e->unit + 1;
-        LCK(lm::launch_streams_step(y, 1, wr, nullptr, nullptr, e->m.eps, nullptr, nullptr, nullptr, M, e->m.width, S(stream)));
+        LCK(lm::launch_streams_step(y, 1, wr, nullptr, nullptr, e->m.eps, nullptr, nullptr, nullptr, M, e->m.width, S(stream), wx));
         return LM_B200_OK;
     }
     if (l.ff != LM_B200_FF_ROUTED_EXPERTS) return LM_B200_EINVAL;

@@ -395,18 +395,26 @@ __global__ void __launch_bounds__(256)
 down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat16* __restrict__ Wd, const int* __restrict__ a_expert,
                          int top, const float* __restrict__ smid, int Sf, const __nv_bfloat16* __restrict__ Wsd,
                          float* __restrict__ x, int D, const float* __restrict__ nw, const float* __restrict__ nb, float alpha,
-                         const TapOut next, const float* __restrict__ a_weight) {
+                         const TapOut next, const float* __restrict__ a_weight, int n_real, const float* __restrict__ ident_h,
+                         const float* __restrict__ shared_gate, int shared_gate_ld) {
     pdl_release();
     const int r = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (n >= D) return;
     float v = 0.f;
-    if (smid) v = warp_dot(smid + (size_t)r * Sf, Wsd + (size_t)n * Sf, Sf, Sf, 1.f, lane, true);
-    else pdl_wait();
+    if (smid) {
+        v = warp_dot(smid + (size_t)r * Sf, Wsd + (size_t)n * Sf, Sf, Sf, 1.f, lane, true);
+        if (shared_gate) v *= sigmoidf_(shared_gate[(size_t)r * shared_gate_ld]);     // one gate number per row
+    } else {
+        pdl_wait();
+    }
     for (int t = 0; t < top; ++t) {
         const int a = r * top + t;
-        const float part = warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
+        // an output beyond the n_real experts is an identity expert: its output is the row's input
+        const float part = (ident_h && a_expert[a] >= n_real)
+                               ? ident_h[(size_t)r * D + n]
+                               : warp_dot(mid + (size_t)a * F, Wd + ((size_t)a_expert[a] * D + n) * F, F, F, 1.f, lane);
         v = a_weight ? fmaf(a_weight[a], part, v) : v + part;
     }
     if (nw) {
@@ -419,14 +427,79 @@ down_combine_rows_kernel(const float* __restrict__ mid, int F, const __nv_bfloat
     }
 }
 
+// Routing of one row by one warp under a GroupedRoute rule.  z [n]: the row's router logits.  scores = softmax(z) over all n
+// outputs; choice scores = scores + correction; with groups, only outputs of the `keep` groups (of n / count neighbours)
+// whose largest choice score is largest can be chosen (ties: the lower group, the lower output); the `top` largest choice
+// scores are taken in descending order and weighed by their scores (without the correction), divided by their sum and
+// times `scale`.  cs [n] and gs [count] are this warp's scratch in shared memory.  out_e / out_w [top].
+__device__ void grouped_route_warp(const float* __restrict__ z, int n, int top, const GroupedRoute& g, float* cs, float* gs,
+                                   int lane, int* __restrict__ out_e, float* __restrict__ out_w) {
+    float m = -CUDART_INF_F;
+    for (int e = lane; e < n; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float den = 0.f;
+    for (int e = lane; e < n; e += 32) den += expf(z[e] - m);
+    den = warp_sum(den);
+    for (int e = lane; e < n; e += 32) cs[e] = expf(z[e] - m) / den + (g.correction ? g.correction[e] : 0.f);
+    __syncwarp();
+    if (g.count > 1 && g.keep < g.count) {
+        const int size = n / g.count;
+        for (int q = lane; q < g.count; q += 32) {
+            float best = -CUDART_INF_F;
+            for (int e = q * size; e < (q + 1) * size; ++e) best = fmaxf(best, cs[e]);
+            gs[q] = best;
+        }
+        __syncwarp();
+        for (int pass = 0; pass < g.keep; ++pass) {           // every lane finds the same group; kept groups are marked
+            float best = -CUDART_INF_F;
+            int bq = -1;
+            for (int q = 0; q < g.count; ++q) {
+                const float v = gs[q];
+                if (v != CUDART_INF_F && (bq < 0 || v > best)) { best = v; bq = q; }
+            }
+            __syncwarp();
+            if (lane == 0 && bq >= 0) gs[bq] = CUDART_INF_F;
+            __syncwarp();
+        }
+        for (int e = lane; e < n; e += 32)
+            if (gs[e / size] != CUDART_INF_F) cs[e] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    float sum = 0.f;
+    for (int t = 0; t < top; ++t) {
+        float best = -CUDART_INF_F;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < n; e += 32) {
+            bool taken = false;
+            for (int u = 0; u < t; ++u) taken |= (out_e[u] == e);
+            const float v = cs[e];
+            if (!taken && (v > best || (v == best && e < bi))) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        const float sc = expf(z[bi] - m) / den;               // the score itself, as computed above
+        sum += sc;
+        if (lane == 0) { out_e[t] = bi; out_w[t] = sc; }
+        __syncwarp();
+    }
+    if (lane == 0)
+        for (int t = 0; t < top; ++t) out_w[t] = out_w[t] / (sum + 1e-20f) * g.scale;
+    __syncwarp();
+}
+
 // One CTA per row: router logits z = h . Wr^T [+ bias] (fp32), the `top` largest in descending order (ties: the lower
 // index), scores sigmoid(z) - or, with softmax_top, the softmax over the chosen logits alone - and the assignment maps of
 // the row kernels: slot r * top + t holds (row r, expert, score).
 __global__ void __launch_bounds__(256)
 router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __restrict__ Wr, int E, int top,
                    float* __restrict__ z_out, int* __restrict__ a_row, float* __restrict__ a_scale, int* __restrict__ a_expert,
-                   int* __restrict__ slot_of, int* __restrict__ n_slots, const float* __restrict__ bias, int softmax_top) {
-    extern __shared__ float zs[];                             // [E]
+                   int* __restrict__ slot_of, int* __restrict__ n_slots, const float* __restrict__ bias, int softmax_top,
+                   const GroupedRoute gr) {
+    extern __shared__ float zs[];                             // [E] (+ [n] + [count] scratch of the grouped rule)
     pdl_release();
     const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     if (warp >= E) pdl_wait();                                // (a warp without an expert may still write the maps below)
@@ -437,6 +510,17 @@ router_rows_kernel(const float* __restrict__ h, int D, const __nv_bfloat16* __re
     __syncthreads();
     if (warp != 0) return;
     if (r == 0 && lane == 0) *n_slots = gridDim.x * top;
+    if (gr.n > 0) {                                           // E = gr.n router outputs (+ the shared unit's gate row)
+        grouped_route_warp(zs, gr.n, top, gr, zs + E, zs + E + gr.n, lane, a_expert + r * top, a_scale + r * top);
+        if (lane == 0)
+            for (int t = 0; t < top; ++t) {
+                const int a = r * top + t;
+                const bool real = a_expert[a] < gr.n_real;    // an identity expert has no products: no row, no slot
+                a_row[a] = real ? r : -1;
+                slot_of[a] = real ? a : -1;
+            }
+        return;
+    }
     float first = 0.f, den = 0.f;                             // softmax over the chosen: the first is the largest
     for (int t = 0; t < top; ++t) {
         float best = -CUDART_INF_F;
@@ -910,11 +994,18 @@ sink_attention_tile_kernel(const float* __restrict__ qk, int q_stride, const flo
 // one warp per row: the `top` largest of z [+ bias] (ties: the lower index) in descending order; scores sigmoid(z), or
 // with softmax_top the softmax over the chosen logits alone
 __global__ void router_topk_kernel(const float* __restrict__ z, int E, int top, int M, int* __restrict__ sel_e,
-                                   float* __restrict__ sel_w, const float* __restrict__ bias, int softmax_top) {
+                                   float* __restrict__ sel_w, const float* __restrict__ bias, int softmax_top,
+                                   const GroupedRoute gr) {
+    extern __shared__ float route_scratch[];                  // grouped rule: [warps][n + count]
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (r >= M) return;
     const float* zr = z + (size_t)r * E;
+    if (gr.n > 0) {                                           // rows of z are E = gr.n (+ 1) wide
+        float* cs = route_scratch + (size_t)(threadIdx.x >> 5) * (gr.n + gr.count);
+        grouped_route_warp(zr, gr.n, top, gr, cs, cs + gr.n, lane, sel_e + (size_t)r * top, sel_w + (size_t)r * top);
+        return;
+    }
     float first = 0.f, den = 0.f;
     for (int t = 0; t < top; ++t) {
         float best = -CUDART_INF_F;
@@ -956,7 +1047,8 @@ __global__ void moe_group_kernel(const int* __restrict__ sel_e, const float* __r
     int* cursor = sh + 2 * E;   // [E]
     for (int e = threadIdx.x; e < E; e += blockDim.x) { count[e] = 0; cursor[e] = 0; }
     __syncthreads();
-    for (int a = threadIdx.x; a < n_assign; a += blockDim.x) atomicAdd(&count[sel_e[a]], 1);
+    for (int a = threadIdx.x; a < n_assign; a += blockDim.x)  // (an output beyond the E experts has no products: no slot)
+        if (sel_e[a] < E) atomicAdd(&count[sel_e[a]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
@@ -972,6 +1064,7 @@ __global__ void moe_group_kernel(const int* __restrict__ sel_e, const float* __r
     __syncthreads();
     for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
         const int e = sel_e[a];
+        if (e >= E) { slot_of[a] = -1; continue; }
         const int s = start[e] + atomicAdd(&cursor[e], 1);
         a_row[s] = a / top;
         a_scale[s] = sel_w[a];
@@ -1129,16 +1222,19 @@ cudaError_t launch_gated_rows(const float* A, int lda, const void* W, long long 
 
 cudaError_t launch_down_combine_rows(const float* mid, int F, const void* Wd, const int* a_expert, int top, const float* smid,
                                      int Sf, const void* Wsd, float* x, int M, int D, const NormW& n, const TapOut& next,
-                                     cudaStream_t st, const float* a_weight) {
+                                     cudaStream_t st, const float* a_weight, int n_real, const float* ident_h,
+                                     const float* shared_gate, int shared_gate_ld) {
     return launch_pdl(down_combine_rows_kernel, dim3((D + 7) / 8, M), dim3(256), 0, st, mid, F,
                       reinterpret_cast<const __nv_bfloat16*>(Wd), a_expert, top, smid, Sf, reinterpret_cast<const __nv_bfloat16*>(Wsd), x,
-                      D, n.w, n.b, n.alpha, next, a_weight);
+                      D, n.w, n.b, n.alpha, next, a_weight, n_real, ident_h, shared_gate, shared_gate_ld);
 }
 
 cudaError_t launch_router_rows(const float* h, int D, const void* Wr, int E, int top, int M, float* z, const GroupMap& gm,
-                               int* slot_of, cudaStream_t st, const float* bias, bool softmax_top) {
-    return launch_pdl(router_rows_kernel, dim3(M), dim3(256), E * sizeof(float), st, h, D, reinterpret_cast<const __nv_bfloat16*>(Wr),
-                      E, top, z, gm.a_row, gm.a_scale, gm.a_expert, slot_of, gm.n_slots, bias, softmax_top ? 1 : 0);
+                               int* slot_of, cudaStream_t st, const float* bias, bool softmax_top, const GroupedRoute* gr) {
+    const GroupedRoute rule = gr ? *gr : GroupedRoute{};
+    return launch_pdl(router_rows_kernel, dim3(M), dim3(256), (size_t)(E + rule.n + rule.count) * sizeof(float), st, h, D,
+                      reinterpret_cast<const __nv_bfloat16*>(Wr), E, top, z, gm.a_row, gm.a_scale, gm.a_expert, slot_of, gm.n_slots,
+                      bias, softmax_top ? 1 : 0, rule);
 }
 
 cudaError_t launch_qk_norm_cache(float* qk, int nq, int nk, const float* qw, const float* kw, float eps, float* kcache,
@@ -1206,8 +1302,10 @@ cudaError_t launch_sink_attention(const float* qk, int q_stride, const float* kc
 }
 
 cudaError_t launch_router_topk(const float* z, int E, int top, int M, int* sel_e, float* sel_w, cudaStream_t st, const float* bias,
-                               bool softmax_top) {
-    router_topk_kernel<<<(M + 3) / 4, 128, 0, st>>>(z, E, top, M, sel_e, sel_w, bias, softmax_top ? 1 : 0);
+                               bool softmax_top, const GroupedRoute* gr) {
+    const GroupedRoute rule = gr ? *gr : GroupedRoute{};
+    router_topk_kernel<<<(M + 3) / 4, 128, (size_t)4 * (rule.n + rule.count) * sizeof(float), st>>>(z, E, top, M, sel_e, sel_w, bias,
+                                                                                                    softmax_top ? 1 : 0, rule);
     return cudaGetLastError();
 }
 

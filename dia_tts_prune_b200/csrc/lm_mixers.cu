@@ -41,7 +41,7 @@ namespace lm {
 __global__ void __launch_bounds__(256)
 layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
                       const float* __restrict__ b, float eps, float out_scale, float* __restrict__ out,
-                      __nv_bfloat16* __restrict__ out_b, int D) {
+                      __nv_bfloat16* __restrict__ out_b, int D, int rms) {
     __shared__ float red[32];
     pdl_release();
     pdl_wait();
@@ -49,7 +49,8 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     const float* xr = x + (size_t)r * D;
     float s = 0.f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) s += xr[c];
-    const float mean = block_sum(s, red) / (float)D;
+    const float total = block_sum(s, red);
+    const float mean = rms ? 0.f : total / (float)D;          // rms: x / sqrt(mean(x^2) + eps), no mean taken off
     float v = 0.f;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         const float d = xr[c] - mean;
@@ -82,14 +83,15 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
 }
 
 __global__ void xielu_rows_kernel(const float* __restrict__ proj, int ld, int off, float ap, float an, float* __restrict__ out,
-                                  int ldo, int out_off, __nv_bfloat16* __restrict__ out_b, int F) {
+                                  int ldo, int out_off, __nv_bfloat16* __restrict__ out_b, int F, int relu2) {
     pdl_release();
     pdl_wait();
     const size_t r = blockIdx.x;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < F; c += gridDim.y * blockDim.x) {
         const float z = proj[r * ld + off + c];
-        const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
-        out[r * ldo + out_off + c] = y;
+        const float y = relu2 ? fmaxf(z, 0.f) * fmaxf(z, 0.f)
+                              : z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+        if (out) out[r * ldo + out_off + c] = y;
         if (out_b) out_b[r * ldo + out_off + c] = __float2bfloat16_rn(y);
     }
 }
@@ -175,7 +177,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
                       int G, int dim, int vdim, const float* __restrict__ talk, const float* __restrict__ sink,
                       const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out, int ldo,
                       __nv_bfloat16* __restrict__ out_b, int M, int TQ, float* __restrict__ part,
-                      unsigned* __restrict__ arrived) {
+                      unsigned* __restrict__ arrived, int window) {
     extern __shared__ __align__(16) float sm[];
     __shared__ bool is_last;
     constexpr int TK = kTalkTK, NT = NW * 32;
@@ -200,7 +202,8 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
     const bool vec_q = (dim % 4 == 0) && (ld % 4 == 0) && (q_off % 4 == 0), vec_k = dim % 4 == 0, vec_v = vdim % 4 == 0;
     // one key/value head whose value pages ARE its key pages (attention over a cached latent): the key tile of a stage
     // serves as its value tile, so a tile of keys is one gather and stays in its buffer through both phases
-    const bool shared_kv = kcache == vcache && G == 1 && dim == vdim;
+    // (a value row may also be the leading vdim channels of a wider key row)
+    const bool shared_kv = kcache == vcache && G == 1 && vdim <= dim;
 
     if (tid < TQ) {
         s_slot[tid] = tid < n_rows ? row_slot[r0 + tid] : -1;
@@ -245,10 +248,11 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
         int seg_b = seg_a + 1;
         while (seg_b < n_rows && s_slot[seg_b] == s_slot[seg_a] && s_pos[seg_b] == s_pos[seg_b - 1] + 1) ++seg_b;
         const int* pages = table + (size_t)s_slot[seg_a] * max_pages;
-        int k_begin = 0, k_end = s_pos[seg_b - 1] + 1;
+        // with a window the segment's first row sees back to its position - window + 1, the later rows less far
+        int k_begin = window > 0 ? max(0, s_pos[seg_a] - window + 1) : 0, k_end = s_pos[seg_b - 1] + 1;
         if (S > 1) {
-            const int per = (k_end + S - 1) / S;
-            k_begin = sp * per;
+            const int per = (k_end - k_begin + S - 1) / S;
+            k_begin += sp * per;
             k_end = min(k_end, k_begin + per);
         }
         // A tile of 64 keys is 2 G stages: the key tiles of the G key/value heads (A), then their value tiles (C).  Stage
@@ -394,7 +398,7 @@ talk_attention_kernel(const float* __restrict__ proj, int ld, int q_off, int gat
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
                         const int jj = lane + 32 * t;
-                        const bool ok = live && jj < jn && j0 + jj <= qi;
+                        const bool ok = live && jj < jn && j0 + jj <= qi && (window <= 0 || qi - (j0 + jj) < window);
                         float v = -CUDART_INF_F;
                         if (ok) {
                             if (talk) {
@@ -573,7 +577,8 @@ __global__ void __launch_bounds__(256)
 delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int H, int G, int dim, int vdim, int taps,
                   const float* __restrict__ cw, const float* __restrict__ tail, const float* __restrict__ a_log,
                   const float* __restrict__ dt_bias, float unit_eps, const int* __restrict__ row_slot,
-                  const int* __restrict__ row_pos, const int* __restrict__ row_start, float* __restrict__ rec, int ldr) {
+                  const int* __restrict__ row_pos, const int* __restrict__ row_start, float* __restrict__ rec, int ldr,
+                  int head_decay_off) {
     extern __shared__ float cbuf[];                           // [C] convolved + silu
     pdl_release();
     pdl_wait();
@@ -602,6 +607,17 @@ delta_prep_kernel(const float* __restrict__ proj, int ld, int beta_off, int H, i
         ss = warp_sum(ss);
         const float inv = (hh < G ? qmul : 1.f) / sqrtf(ss + unit_eps);
         for (int c = lane; c < dim; c += 32) dst[hh * dim + c] = src[c] * inv;
+    }
+    if (head_decay_off >= 0) {
+        // one decay per head, its pre-activation a column of the stacked projections; the output gate stays where it is.
+        // rec row: q (G dim) | k (G dim) | v (H vdim) | decay (H) | beta (H)
+        const int v0 = 2 * G * dim, d0 = v0 + H * vdim, b0 = d0 + H;
+        for (int c = tid; c < H * vdim; c += blockDim.x) dst[v0 + c] = cbuf[v0 + c];
+        for (int h = tid; h < H; h += blockDim.x) {
+            dst[d0 + h] = expf(-expf(a_log[h]) * softplusf_(row[head_decay_off + h] + dt_bias[h]));
+            dst[b0 + h] = sigmoidf_(row[beta_off + h]);
+        }
+        return;
     }
     const int v0 = 2 * G * dim, d0 = v0 + H * vdim, g0 = d0 + H * dim, b0 = g0 + H * vdim;
     for (int c = tid; c < H * vdim; c += blockDim.x) {
@@ -671,7 +687,7 @@ __global__ void __launch_bounds__(kScanThreads)
 column_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int a_off, int v_off, int beta_off, int H, int G,
                    int dim, int vdim, float* __restrict__ state, const int* __restrict__ seq_slot,
                    const int* __restrict__ seq_row0, const int* __restrict__ seq_count, const int* __restrict__ row_pos,
-                   float* __restrict__ o, int ldo) {
+                   float* __restrict__ o, int ldo, int head_decay) {
     extern __shared__ float sh[];
     constexpr int DS = 8 * RP;                                // staged row length (channels beyond dim hold zeros)
     float* sq = sh;                                           // [TT][DS]
@@ -710,7 +726,8 @@ column_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, i
         for (int i = 0; i < RP; ++i) {
             const bool ok = src[i] >= 0 && (tid + kScanThreads * i) / DS < nt;
             rq[i] = ok ? base[src[i] + q_off + qh * dim] : 0.f;
-            ra[i] = ok ? base[src[i] + a_off + h * dim] : 0.f;
+            // head_decay: column a_off + h of the row holds the one decay of all of the head's key channels
+            ra[i] = !ok ? 0.f : head_decay ? base[((tid + kScanThreads * i) / DS) * ld + a_off + h] : base[src[i] + a_off + h * dim];
             if (DELTA) rk[i] = ok ? base[src[i] + k_off + g * dim] : 0.f;
         }
 #pragma unroll
@@ -809,7 +826,8 @@ template <int RP>
 __global__ void __launch_bounds__(kScanThreads)
 scalar_gate_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_off, int a_off, int v_off, int b_off, int H, int dim,
                         int vdim, float* __restrict__ state, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
-                        const int* __restrict__ seq_count, const int* __restrict__ row_pos, float* __restrict__ o, int ldo) {
+                        const int* __restrict__ seq_count, const int* __restrict__ row_pos, float* __restrict__ o, int ldo,
+                        const float* __restrict__ fixed_decay, int normaliser) {
     extern __shared__ float sh[];
     constexpr int DS = 8 * RP;
     float* sq = sh;                                           // [TT][DS]
@@ -819,11 +837,13 @@ scalar_gate_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_o
     float* sb = sa + kScanTT;                                 // [TT]
     pdl_release();
     pdl_wait();
-    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kScanCols, vcols = vdim + 1;
+    // fixed_decay: a = fixed_decay[h] and b = 1 for every token (no gate columns are read); normaliser 0: vdim columns
+    const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kScanCols, vcols = vdim + (normaliser ? 1 : 0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, part = lane & 7, cl = warp * 4 + (lane >> 3);
     const int col = col0 + cl;
     const int slot = seq_slot[s], row0 = seq_row0[s], n = seq_count[s], start = row_pos[row0];
     const bool col_ok = col < vcols;
+    const float a_fix = fixed_decay ? fixed_decay[h] : 0.f;
     float* st = state + (((size_t)slot * H + h) * vcols + (col_ok ? col : 0)) * dim;
     float S[RP];
 #pragma unroll
@@ -850,11 +870,11 @@ scalar_gate_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_o
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int idx = tid + kScanThreads * i, t = idx / kScanCols, c = col0 + (idx - t * kScanCols);
-            rv[i] = t < nt ? (c < vdim ? base[(size_t)t * ld + v_off + h * vdim + c] : (c == vdim ? 1.f : 0.f)) : 0.f;
+            rv[i] = t < nt ? (c < vdim ? base[(size_t)t * ld + v_off + h * vdim + c] : ((c == vdim && normaliser) ? 1.f : 0.f)) : 0.f;
         }
         if (tid < nt) {
-            ra = base[(size_t)tid * ld + a_off + h];
-            rb = base[(size_t)tid * ld + b_off + h];
+            ra = fixed_decay ? a_fix : base[(size_t)tid * ld + a_off + h];
+            rb = fixed_decay ? 1.f : base[(size_t)tid * ld + b_off + h];
         }
     };
     fetch(0);
@@ -906,8 +926,9 @@ scalar_gate_scan_kernel(const float* __restrict__ in, int ld, int q_off, int k_o
 }
 
 // o[r][h] <- o[r][h] / sqrt(mean(o[r][h]^2) + eps) * w [* gate[r][h]] in place (one warp per row and head), and its bf16 copy
+// gate_act: 0 the gate columns are used as they are (already activated), 1 sigmoid, 2 silu of them; w may be absent
 __global__ void head_norm_gate_kernel(float* __restrict__ o, int ldo, __nv_bfloat16* __restrict__ o_b, const float* __restrict__ w,
-                                      const float* __restrict__ gate, int ldg, int H, int vdim, float eps, int M) {
+                                      const float* __restrict__ gate, int ldg, int H, int vdim, float eps, int M, int gate_act) {
     pdl_release();
     pdl_wait();
     const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -919,8 +940,11 @@ __global__ void head_norm_gate_kernel(float* __restrict__ o, int ldo, __nv_bfloa
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
     for (int c = lane; c < vdim; c += 32) {
-        float y = row[c] * inv * w[c];
-        if (gate) y *= gate[(size_t)r * ldg + (size_t)h * vdim + c];
+        float y = row[c] * inv * (w ? w[c] : 1.f);
+        if (gate) {
+            const float gz = gate[(size_t)r * ldg + (size_t)h * vdim + c];
+            y *= gate_act == 1 ? sigmoidf_(gz) : gate_act == 2 ? siluf_(gz) : gz;
+        }
         row[c] = y;
         if (o_b) o_b[(size_t)r * ldo + (size_t)h * vdim + c] = __float2bfloat16_rn(y);
     }
@@ -928,9 +952,9 @@ __global__ void head_norm_gate_kernel(float* __restrict__ o, int ldo, __nv_bfloa
 
 // ---- launchers --------------------------------------------------------------------------------------------------------
 cudaError_t launch_layernorm_rows(const float* x, const int* rows, const float* w, const float* b, float eps, float out_scale,
-                                  float* out, void* out_bf16, int M, int D, cudaStream_t st) {
+                                  float* out, void* out_bf16, int M, int D, cudaStream_t st, bool rms) {
     return launch_pdl(layernorm_rows_kernel, dim3(M), dim3(256), 0, st, x, rows, w, b, eps, out_scale, out,
-                      reinterpret_cast<__nv_bfloat16*>(out_bf16), D);
+                      reinterpret_cast<__nv_bfloat16*>(out_bf16), D, rms ? 1 : 0);
 }
 
 cudaError_t launch_pair_rows(const float* x, const float* x0, float* cat, void* cat_bf16, int M, int D, cudaStream_t st) {
@@ -944,9 +968,9 @@ cudaError_t launch_add_rows(float* x, const float* y, int M, int D, cudaStream_t
 }
 
 cudaError_t launch_xielu_rows(const float* proj, int ld, int off, float ap, float an, float* out, int ldo, int out_off,
-                              void* out_bf16, int M, int F, cudaStream_t st) {
+                              void* out_bf16, int M, int F, cudaStream_t st, bool relu2) {
     return launch_pdl(xielu_rows_kernel, dim3(M, F > 1024 ? (F + 1023) / 1024 : 1), dim3(256), 0, st, proj, ld, off, ap, an, out,
-                      ldo, out_off, reinterpret_cast<__nv_bfloat16*>(out_bf16), F);
+                      ldo, out_off, reinterpret_cast<__nv_bfloat16*>(out_bf16), F, relu2 ? 1 : 0);
 }
 
 cudaError_t launch_talk_prep(float* proj, int ld, const float* bias, int q_off, int k_off, int v_off, int gate_off,
@@ -980,7 +1004,7 @@ static cudaError_t launch_talk_inst(const float* proj, int ld, int q_off, int ga
     }
     return launch_pdl(talk_attention_kernel<VU, NP, NW>, dim3((M + TQ - 1) / TQ, S), dim3(NW * 32), smem, st, proj, ld, q_off,
                       gate_off, kcache, vcache, pm.table, pm.max_pages, pm.page_size, a.heads, a.kv_heads, a.dim, a.vdim, a.talk,
-                      a.sink, rm.slot, rm.pos, out, ldo, out_b, M, TQ, part, arrived);
+                      a.sink, rm.slot, rm.pos, out, ldo, out_b, M, TQ, part, arrived, a.window);
 }
 
 // the most pairs (heads x rows of a tile) a CTA carries: 128, 64 with values wider than 128 (accumulators per thread)
@@ -1026,7 +1050,7 @@ cudaError_t launch_talk_attention(const float* proj, int ld, int q_off, int gate
 }
 
 cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, const DeltaShape& d, const float* tail, const RowMeta& rm,
-                              float* rec, int ldr, int M, cudaStream_t st) {
+                              float* rec, int ldr, int M, cudaStream_t st, int head_decay_off) {
     if (d.taps < 1 || d.taps > kMaxTaps) return cudaErrorNotSupported;
     const int C = 2 * d.kv_heads * d.dim + d.heads * d.vdim;
     const size_t smem = (size_t)C * 4;
@@ -1035,7 +1059,7 @@ cudaError_t launch_delta_prep(const float* proj, int ld, int beta_off, const Del
         if (e != cudaSuccess) return e;
     }
     return launch_pdl(delta_prep_kernel, dim3(M), dim3(256), smem, st, proj, ld, beta_off, d.heads, d.kv_heads, d.dim, d.vdim, d.taps,
-                      d.conv_w, tail, d.a_log, d.dt_bias, d.unit_eps, rm.slot, rm.pos, rm.start, rec, ldr);
+                      d.conv_w, tail, d.a_log, d.dt_bias, d.unit_eps, rm.slot, rm.pos, rm.start, rec, ldr, head_decay_off);
 }
 
 cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* tail, const SeqMeta& sm, int n_seq,
@@ -1047,7 +1071,8 @@ cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* 
 
 template <int RP, bool DELTA>
 static cudaError_t launch_scan_inst(const float* in, int ld, const ScanInputs& si, int H, int G, int dim, int vdim, float* state,
-                                    const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st) {
+                                    const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
+                                    bool head_decay) {
     const size_t smem = (size_t)((DELTA ? 3 : 2) * kScanTT * 8 * RP + kScanTT * kScanCols + kScanTT) * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(column_scan_kernel<RP, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1055,7 +1080,7 @@ static cudaError_t launch_scan_inst(const float* in, int ld, const ScanInputs& s
     }
     return launch_pdl(column_scan_kernel<RP, DELTA>, dim3(n_seq, H, (vdim + kScanCols - 1) / kScanCols), dim3(kScanThreads), smem, st,
                       in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, G, dim, vdim, state, sm.slot, sm.row0,
-                      sm.count, rm.pos, o, ldo);
+                      sm.count, rm.pos, o, ldo, head_decay ? 1 : 0);
 }
 
 cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_off, const float* bias, const float* lower, int n_qf,
@@ -1066,11 +1091,11 @@ cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_of
 // delta: the delta rule (reads k and beta); otherwise the gate-tied write (its inputs prepared by launch_gate_prep)
 cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
                                float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
-                               cudaStream_t st) {
+                               cudaStream_t st, bool head_decay) {
     if (dim > 256 || H % G || H > 65535) return cudaErrorNotSupported;
 #define SCAN_CASE(RP)                                                                                                    \
-    return delta ? launch_scan_inst<RP, true>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st)             \
-                 : launch_scan_inst<RP, false>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st)
+    return delta ? launch_scan_inst<RP, true>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st, head_decay) \
+                 : launch_scan_inst<RP, false>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st, head_decay)
     if (dim <= 32) SCAN_CASE(4);
     if (dim <= 64) SCAN_CASE(8);
     if (dim <= 128) SCAN_CASE(16);
@@ -1080,30 +1105,32 @@ cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bo
 
 template <int RP>
 static cudaError_t launch_scalar_scan_inst(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
-                                           const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st) {
+                                           const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
+                                           const float* fixed_decay, bool normaliser) {
     const size_t smem = (size_t)(2 * kScanTT * 8 * RP + kScanTT * kScanCols + 2 * kScanTT) * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(scalar_gate_scan_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(scalar_gate_scan_kernel<RP>, dim3(n_seq, H, (vdim + 1 + kScanCols - 1) / kScanCols), dim3(kScanThreads), smem,
-                      st, in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, dim, vdim, state, sm.slot, sm.row0, sm.count,
-                      rm.pos, o, ldo);
+    return launch_pdl(scalar_gate_scan_kernel<RP>, dim3(n_seq, H, (vdim + (normaliser ? 1 : 0) + kScanCols - 1) / kScanCols),
+                      dim3(kScanThreads), smem, st, in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, dim, vdim, state,
+                      sm.slot, sm.row0, sm.count, rm.pos, o, ldo, fixed_decay, normaliser ? 1 : 0);
 }
 
 cudaError_t launch_scalar_gate_scan(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
-                                    const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st) {
+                                    const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
+                                    const float* fixed_decay, bool normaliser) {
     if (dim > 256 || H > 65535) return cudaErrorNotSupported;
-    if (dim <= 32) return launch_scalar_scan_inst<4>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
-    if (dim <= 64) return launch_scalar_scan_inst<8>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
-    if (dim <= 128) return launch_scalar_scan_inst<16>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
-    return launch_scalar_scan_inst<32>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st);
+    if (dim <= 32) return launch_scalar_scan_inst<4>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
+    if (dim <= 64) return launch_scalar_scan_inst<8>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
+    if (dim <= 128) return launch_scalar_scan_inst<16>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
+    return launch_scalar_scan_inst<32>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
 }
 
 cudaError_t launch_head_norm_gate(float* o, int ldo, void* o_bf16, const float* w, const float* gate, int ldg, int H, int vdim,
-                                  float eps, int M, cudaStream_t st) {
+                                  float eps, int M, cudaStream_t st, int gate_act) {
     return launch_pdl(head_norm_gate_kernel, dim3((M * H + 7) / 8), dim3(256), 0, st, o, ldo, reinterpret_cast<__nv_bfloat16*>(o_bf16),
-                      w, gate, ldg, H, vdim, eps, M);
+                      w, gate, ldg, H, vdim, eps, M, gate_act);
 }
 
 }  // namespace lm

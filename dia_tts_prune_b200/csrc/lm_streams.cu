@@ -37,14 +37,25 @@ constexpr int kMaxStreams = 8;
 
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void streams_embed_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids, float scale,
-                                     float* __restrict__ X, int streams, int V, int D) {
+                                     const float* __restrict__ norm_w, float eps, float* __restrict__ X, int streams, int V, int D) {
+    __shared__ float red[32];
     pdl_release();
     pdl_wait();
     const int r = blockIdx.x;
     const int id = ids[r];
     const bool ok = id >= 0 && id < V;
+    float inv = 1.f;
+    if (norm_w) {                                             // x / sqrt(mean(x^2) + eps) * w on the scaled row
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < D; c += blockDim.x) {
+            const float v = ok ? bf(table[(size_t)id * D + c]) * scale : 0.f;
+            ss = fmaf(v, v, ss);
+        }
+        inv = 1.0f / sqrtf(block_sum(ss, red) / (float)D + eps);
+    }
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        const float v = ok ? bf(table[(size_t)id * D + c]) * scale : 0.f;
+        float v = ok ? bf(table[(size_t)id * D + c]) * scale : 0.f;
+        if (norm_w) v = v * inv * norm_w[c];
         for (int j = 0; j < streams; ++j) X[((size_t)r * streams + j) * D + c] = v;
     }
 }
@@ -57,10 +68,11 @@ __global__ void __launch_bounds__(256)
 streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const float* __restrict__ out,
                     const float* __restrict__ y, const float* __restrict__ parts, const int* __restrict__ slot_of,
                     const float* __restrict__ sel_w, int top, const float* __restrict__ in, const float* __restrict__ norm_w,
-                    float eps, const int* __restrict__ rows, float* __restrict__ h, __nv_bfloat16* __restrict__ h_b, int D) {
+                    float eps, const int* __restrict__ rows, float* __restrict__ h, __nv_bfloat16* __restrict__ h_b, int D,
+                    const StreamExtra ex) {
     extern __shared__ __align__(16) float u_s[];              // [D]
     __shared__ float red[32];
-    __shared__ float mix_s[S * S], out_s[S], in_s[S];
+    __shared__ float mix_s[S * S], out_s[S], in_s[S], out2_s[S];
     pdl_release();
     constexpr int s = S;
     const int tid = threadIdx.x;
@@ -68,6 +80,7 @@ streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const 
     if (tid < s * s) mix_s[tid] = write ? mix[tid] : 0.f;
     if (tid < s) {
         out_s[tid] = write ? out[tid] : 0.f;
+        out2_s[tid] = (write && ex.y2) ? ex.out2[tid] : 0.f;
         in_s[tid] = in ? in[tid] : 1.f;
     }
     pdl_wait();
@@ -101,14 +114,24 @@ streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const 
 #pragma unroll
             for (int e = 0; e < VW; ++e) yv[e] = 0.f;
             if (y) load(y + (size_t)r * D + c, yv);
+            if (ex.y_gate) {                                  // one gate number per row on the unit's output
+                const float gt = sigmoidf_(ex.y_gate[(size_t)r * ex.y_gate_ld]);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) yv[e] *= gt;
+            }
             if (parts)
                 for (int t = 0; t < top; ++t) {
                     float pv[VW];
-                    load(parts + (size_t)slot_of[(size_t)r * top + t] * D + c, pv);
+                    const int slot = slot_of[(size_t)r * top + t];    // < 0: an identity expert, its output is the input row
+                    load(slot >= 0 ? parts + (size_t)slot * D + c : ex.ident_h + (size_t)r * D + c, pv);
                     const float wt = sel_w[(size_t)r * top + t];
 #pragma unroll
                     for (int e = 0; e < VW; ++e) yv[e] = fmaf(wt, pv[e], yv[e]);
                 }
+            float y2v[VW];
+#pragma unroll
+            for (int e = 0; e < VW; ++e) y2v[e] = 0.f;
+            if (ex.y2) load(ex.y2 + (size_t)r * D + c, y2v);  // the other sublayer's output of a parallel record
             float nx[S][VW];
 #pragma unroll
             for (int j = 0; j < S; ++j) {
@@ -123,7 +146,7 @@ streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const 
                             for (int e = 0; e < VW; ++e) nx[j][e] = fmaf(mw, xs[i][e], nx[j][e]);
                         }
 #pragma unroll
-                    for (int e = 0; e < VW; ++e) nx[j][e] = fmaf(out_s[j], yv[e], nx[j][e]);
+                    for (int e = 0; e < VW; ++e) nx[j][e] = fmaf(out_s[j], yv[e], fmaf(out2_s[j], y2v[e], nx[j][e]));
                     store(xr + (size_t)j * D + c, nx[j]);
                 }
             }
@@ -156,7 +179,8 @@ streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const 
             }
         return;
     }
-    const float mean = block_sum(sum, red) / (float)D;
+    const float total = block_sum(sum, red);
+    const float mean = ex.rms ? 0.f : total / (float)D;       // the RMS norm takes no mean off
     float v = 0.f;
     for (int c = tid; c < D; c += blockDim.x) {
         const float d = u_s[c] - mean;
@@ -164,19 +188,47 @@ streams_step_kernel(float* __restrict__ X, const float* __restrict__ mix, const 
     }
     const float inv = 1.0f / sqrtf(block_sum(v, red) / (float)D + eps);
     for (int c = tid; c < D; c += blockDim.x) {
-        const float o = (u_s[c] - mean) * inv * norm_w[c];
+        const float n = (u_s[c] - mean) * inv, o = n * norm_w[c];
         h[(size_t)blockIdx.x * D + c] = o;
         if (h_b) h_b[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(o);
+        if (ex.norm_w2) {                                     // a second weight on the same statistics: the other sublayer's input
+            const float o2 = n * ex.norm_w2[c];
+            ex.h2[(size_t)blockIdx.x * D + c] = o2;
+            if (ex.h2_b) reinterpret_cast<__nv_bfloat16*>(ex.h2_b)[(size_t)blockIdx.x * D + c] = __float2bfloat16_rn(o2);
+        }
     }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One CTA per row.  pages: [page][page_size][kv_rank].
+// turns the pair (a, b) by angle pos * f
+__device__ __forceinline__ void turn_pair(float& a, float& b, int pos, float f) {
+    float sn, cs;
+    sincosf((float)pos * f, &sn, &cs);
+    const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+    a = ra;
+    b = rb;
+}
+// the partner of channel c of a vector whose first rot_dims channels turn: pairs (2i, 2i + 1) or (i, i + rot_dims / 2);
+// `first`: whether c is the pair's first member; `i`: the pair's index
+__device__ __forceinline__ int rot_partner(int c, int rot_dims, int half_layout, bool& first, int& i) {
+    if (half_layout) {
+        const int hf = rot_dims >> 1;
+        first = c < hf;
+        i = first ? c : c - hf;
+        return first ? c + hf : c - hf;
+    }
+    first = (c & 1) == 0;
+    i = c >> 1;
+    return first ? c + 1 : c - 1;
+}
+
+// One CTA per row.  pages: [page][page_size][kv_rank + rot.n]: the normed latent, then (rot.n > 0) the columns
+// c_off + kv_rank .. of the row, not normed, their first rot.dims channels turned with the row's position.
 __global__ void __launch_bounds__(256)
 latent_prep_kernel(float* __restrict__ proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* __restrict__ qw,
                    const float* __restrict__ cw, float eps, __nv_bfloat16* __restrict__ cq_b, float* __restrict__ pages,
                    const int* __restrict__ table, int max_pages, int page_size, const int* __restrict__ row_slot,
-                   const int* __restrict__ row_pos) {
+                   const int* __restrict__ row_pos, const RotPart rot) {
     __shared__ float red[32];
     pdl_release();
     pdl_wait();
@@ -195,8 +247,51 @@ latent_prep_kernel(float* __restrict__ proj, int ld, int q_off, int q_rank, int 
     const float cinv = 1.0f / sqrtf(block_sum(ss, red) / (float)kv_rank + eps);
     const int pos = row_pos[r];
     const int page = table[(size_t)row_slot[r] * max_pages + pos / page_size];
-    float* dst = pages + ((size_t)page * page_size + pos % page_size) * kv_rank;
+    float* dst = pages + ((size_t)page * page_size + pos % page_size) * (kv_rank + rot.n);
     for (int c = tid; c < kv_rank; c += blockDim.x) dst[c] = row[c_off + c] * cinv * cw[c];
+    const float* kr = row + c_off + kv_rank;
+    for (int c = tid; c < rot.n; c += blockDim.x) {
+        float v = kr[c];
+        if (c < rot.dims) {
+            bool first;
+            int i;
+            const int o = rot_partner(c, rot.dims, rot.half_layout, first, i);
+            float a = first ? v : kr[o], b = first ? kr[o] : v;
+            turn_pair(a, b, pos, rot.freq[i]);
+            v = first ? a : b;
+        }
+        dst[kv_rank + c] = v;
+    }
+}
+
+// dst[r][d_off + h dhs + c] = scale_h * turned(src[r][s_off + h shs + c]), c < n, for H heads per row: the first rot.dims
+// channels turn with the row's position, the others pass.  Heads below `split` take scale_a, the others scale_b.  In place
+// when dst == src with equal strides (a thread owns both members of a pair).
+__global__ void __launch_bounds__(256)
+rot_rows_kernel(const float* __restrict__ src, int lds, int s_off, int shs, float* __restrict__ dst, int ldd, int d_off, int dhs,
+                int H, int n, int rot_dims, int half_layout, const float* __restrict__ freq, int split, float scale_a,
+                float scale_b, const int* __restrict__ row_pos) {
+    pdl_release();
+    pdl_wait();
+    const int r = blockIdx.x, pos = row_pos[r], np = rot_dims >> 1, per = np + (n - rot_dims);   // items per head
+    const float* in = src + (size_t)r * lds + s_off;
+    float* out = dst + (size_t)r * ldd + d_off;
+    for (int idx = threadIdx.x; idx < H * per; idx += blockDim.x) {
+        const int h = idx / per, it = idx - h * per;
+        const float sc = h < split ? scale_a : scale_b;
+        const float* ih = in + (size_t)h * shs;
+        float* oh = out + (size_t)h * dhs;
+        if (it < np) {
+            const int c0 = half_layout ? it : 2 * it, c1 = half_layout ? it + np : 2 * it + 1;
+            float a = ih[c0], b = ih[c1];
+            turn_pair(a, b, pos, freq[it]);
+            oh[c0] = a * sc;
+            oh[c1] = b * sc;
+        } else {
+            const int c = rot_dims + (it - np);
+            oh[c] = ih[c] * sc;
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -209,30 +304,31 @@ constexpr int kLatentWarps = 8;
 
 __global__ void __launch_bounds__(kLatentWarps * 32)
 latent_attention_rows_kernel(const float* __restrict__ q, const float* __restrict__ pages, const int* __restrict__ table,
-                             int max_pages, int page_size, int H, int R, const float* __restrict__ sink,
+                             int max_pages, int page_size, int H, int R, int RK, int window, const float* __restrict__ sink,
                              const int* __restrict__ row_slot, const int* __restrict__ row_pos, float* __restrict__ out) {
-    extern __shared__ float sm[];                             // q [R] | per warp: sums [R], maximum, denominator
+    extern __shared__ float sm[];                             // q [RK] | per warp: sums [R], maximum, denominator
     float* qs = sm;
-    float* part = sm + R;
+    float* part = sm + RK;
     pdl_release();
     pdl_wait();
     const int r = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = row_pos[r];
     const int* pg = table + (size_t)row_slot[r] * max_pages;
-    for (int c = threadIdx.x; c < R; c += blockDim.x) qs[c] = q[((size_t)r * H + h) * R + c];
+    for (int c = threadIdx.x; c < RK; c += blockDim.x) qs[c] = q[((size_t)r * H + h) * RK + c];
     __syncthreads();
     float acc[kLatentPerLane];
 #pragma unroll
     for (int u = 0; u < kLatentPerLane; ++u) acc[u] = 0.f;
     float m = -CUDART_INF_F, l = 0.f;
-    for (int j = warp; j <= pos; j += kLatentWarps) {
-        const float* c = pages + ((size_t)pg[j / page_size] * page_size + j % page_size) * R;
+    const int j_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    for (int j = j_lo + warp; j <= pos; j += kLatentWarps) {
+        const float* c = pages + ((size_t)pg[j / page_size] * page_size + j % page_size) * RK;
         float cv[kLatentPerLane], sc = 0.f;
 #pragma unroll
-        for (int u = 0; u < kLatentPerLane; ++u) {
+        for (int u = 0; u < kLatentPerLane; ++u) {            // keys are the RK channels, values the first R of them
             const int ch = lane + 32 * u;
-            cv[u] = ch < R ? c[ch] : 0.f;
-            sc = fmaf(ch < R ? qs[ch] : 0.f, cv[u], sc);
+            cv[u] = ch < RK ? c[ch] : 0.f;
+            sc = fmaf(ch < RK ? qs[ch] : 0.f, cv[u], sc);
         }
         sc = warp_sum(sc);
         const float mn = fmaxf(m, sc), corr = expf(m - mn), p = expf(sc - mn);
@@ -273,15 +369,16 @@ constexpr int HB = 64, HK = 16;
 
 __global__ void __launch_bounds__(256)
 head_linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, float* __restrict__ Y, int ldy,
-                        __nv_bfloat16* __restrict__ Yb, int M, int N, int K, float alpha, const float* __restrict__ gate, int ldg) {
+                        __nv_bfloat16* __restrict__ Yb, int M, int N, int K, float alpha, const float* __restrict__ gate, int ldg,
+                        int a_hs, int y_hs) {
     __shared__ __align__(16) float As[HK][HB + 4];
     __shared__ __align__(16) float Bs[HK][HB + 4];
     const int hd = blockIdx.z, m0 = blockIdx.y * HB, n0 = blockIdx.x * HB;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int lr = tid >> 2, lk = (tid & 3) * 4;
-    const float* arow = (m0 + lr < M) ? A + (size_t)(m0 + lr) * lda + (size_t)hd * K : nullptr;
+    const float* arow = (m0 + lr < M) ? A + (size_t)(m0 + lr) * lda + (size_t)hd * a_hs : nullptr;
     const __nv_bfloat16* wrow = (n0 + lr < N) ? W + ((size_t)hd * N + n0 + lr) * K : nullptr;
-    const bool a_vec = (lda % 4 == 0) && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    const bool a_vec = (lda % 4 == 0) && (K % 4 == 0) && (a_hs % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
     const bool w_vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 7) == 0);
     float acc[4][4];
 #pragma unroll
@@ -339,8 +436,8 @@ head_linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat1
             if (n >= N) continue;
             float v = acc[i][j] * alpha;
             if (gate) v *= sigmoidf_(gate[(size_t)m * ldg + (size_t)hd * N + n]);
-            Y[(size_t)m * ldy + (size_t)hd * N + n] = v;
-            if (Yb) Yb[(size_t)m * ldy + (size_t)hd * N + n] = __float2bfloat16_rn(v);
+            Y[(size_t)m * ldy + (size_t)hd * y_hs + n] = v;
+            if (Yb) Yb[(size_t)m * ldy + (size_t)hd * y_hs + n] = __float2bfloat16_rn(v);
         }
     }
 }
@@ -348,19 +445,20 @@ head_linear_tile_kernel(const float* __restrict__ A, int lda, const __nv_bfloat1
 // the same for a handful of rows: one warp per output element, the weights stream once per row
 __global__ void __launch_bounds__(256)
 head_linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, float* __restrict__ Y, int ldy,
-                        __nv_bfloat16* __restrict__ Yb, int H, int N, int K, float alpha, const float* __restrict__ gate, int ldg) {
+                        __nv_bfloat16* __restrict__ Yb, int H, int N, int K, float alpha, const float* __restrict__ gate, int ldg,
+                        int a_hs, int y_hs) {
     pdl_release();
     const int m = blockIdx.y, lane = threadIdx.x & 31;
     const int col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (col >= H * N) return;
     const int hd = col / N;
     const __nv_bfloat16* wrow = W + (size_t)col * K;          // W[h][n][k] is row h N + n of a [H N][K] matrix
-    const bool vec = (K % 4 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 7) == 0) &&
+    const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (a_hs % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 7) == 0) &&
                      ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
     uint2 w0 = make_uint2(0u, 0u);
     if (vec && lane * 4 < K) w0 = *reinterpret_cast<const uint2*>(wrow + lane * 4);
     pdl_wait();
-    const float* arow = A + (size_t)m * lda + (size_t)hd * K;
+    const float* arow = A + (size_t)m * lda + (size_t)hd * a_hs;
     float acc = 0.f;
     if (vec) {
         for (int k = lane * 4; k < K; k += 128) {
@@ -379,8 +477,9 @@ head_linear_rows_kernel(const float* __restrict__ A, int lda, const __nv_bfloat1
     if (lane == 0) {
         float v = acc * alpha;
         if (gate) v *= sigmoidf_(gate[(size_t)m * ldg + col]);
-        Y[(size_t)m * ldy + col] = v;
-        if (Yb) Yb[(size_t)m * ldy + col] = __float2bfloat16_rn(v);
+        const size_t at = (size_t)m * ldy + (size_t)hd * y_hs + (col - hd * N);
+        Y[at] = v;
+        if (Yb) Yb[at] = __float2bfloat16_rn(v);
     }
 }
 
@@ -462,19 +561,19 @@ mlstm_finish_kernel(const float* __restrict__ raw, int ldr, const float* __restr
 
 // ---- launchers --------------------------------------------------------------------------------------------------------
 cudaError_t launch_streams_embed(const void* table, const int* ids, float scale, float* X, int streams, int M, int V, int D,
-                                 cudaStream_t st) {
-    return launch_pdl(streams_embed_kernel, dim3(M), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(table), ids, scale, X,
-                      streams, V, D);
+                                 cudaStream_t st, const float* norm_w, float eps) {
+    return launch_pdl(streams_embed_kernel, dim3(M), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(table), ids, scale,
+                      norm_w, eps, X, streams, V, D);
 }
 
 cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, const float* in, const float* norm_w, float eps,
-                                const int* rows, float* h, void* h_bf16, int M, int D, cudaStream_t st) {
+                                const int* rows, float* h, void* h_bf16, int M, int D, cudaStream_t st, const StreamExtra& ex) {
     if (streams < 1 || streams > kMaxStreams) return cudaErrorNotSupported;
     const size_t smem = (size_t)D * 4;
     auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-    const bool vec = D % 4 == 0 && aligned(X) && aligned(wr.y) && aligned(wr.parts);
+    const bool vec = D % 4 == 0 && aligned(X) && aligned(wr.y) && aligned(wr.parts) && aligned(ex.y2) && aligned(ex.ident_h);
     using Kernel = void (*)(float*, const float*, const float*, const float*, const float*, const int*, const float*, int, const float*,
-                            const float*, float, const int*, float*, __nv_bfloat16*, int);
+                            const float*, float, const int*, float*, __nv_bfloat16*, int, const StreamExtra);
     Kernel kernel = nullptr;
     switch (streams) {
 #define STREAMS_CASE(S) case S: kernel = vec ? streams_step_kernel<4, S> : streams_step_kernel<1, S>; break
@@ -494,40 +593,51 @@ cudaError_t launch_streams_step(float* X, int streams, const StreamWrite& wr, co
         }
     }
     return launch_pdl(kernel, dim3(M), dim3(256), smem, st, X, wr.mix, wr.out, wr.y, wr.parts, wr.slot_of, wr.sel_w, wr.top,
-                      in, norm_w, eps, rows, h, reinterpret_cast<__nv_bfloat16*>(h_bf16), D);
+                      in, norm_w, eps, rows, h, reinterpret_cast<__nv_bfloat16*>(h_bf16), D, ex);
 }
 
 cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c_off, int kv_rank, const float* qw,
                                const float* cw, float eps, void* cq_bf16, float* pages, const PageMap& pm, const RowMeta& rm,
-                               int M, cudaStream_t st) {
+                               int M, cudaStream_t st, const RotPart& rot) {
+    if (rot.n < 0 || rot.dims < 0 || rot.dims % 2 || rot.dims > rot.n || (rot.dims > 0 && !rot.freq)) return cudaErrorInvalidValue;
     return launch_pdl(latent_prep_kernel, dim3(M), dim3(256), 0, st, proj, ld, q_off, q_rank, c_off, kv_rank, qw, cw, eps,
-                      reinterpret_cast<__nv_bfloat16*>(cq_bf16), pages, pm.table, pm.max_pages, pm.page_size, rm.slot, rm.pos);
+                      reinterpret_cast<__nv_bfloat16*>(cq_bf16), pages, pm.table, pm.max_pages, pm.page_size, rm.slot, rm.pos, rot);
+}
+
+cudaError_t launch_rot_rows(const float* src, int lds, int s_off, int shs, float* dst, int ldd, int d_off, int dhs, int H, int n,
+                            const RotPart& rot, int split, float scale_a, float scale_b, const RowMeta& rm, int M, cudaStream_t st) {
+    if (rot.dims < 0 || rot.dims % 2 || rot.dims > n || (rot.dims > 0 && !rot.freq)) return cudaErrorInvalidValue;
+    return launch_pdl(rot_rows_kernel, dim3(M), dim3(256), 0, st, src, lds, s_off, shs, dst, ldd, d_off, dhs, H, n, rot.dims,
+                      rot.half_layout, rot.freq, split, scale_a, scale_b, rm.pos);
 }
 
 bool latent_attention_rows_supported(int H, int R) { return H > 0 && H <= 65535 && R > 0 && R <= 32 * kLatentPerLane; }
 
 cudaError_t launch_latent_attention_rows(const float* q, const float* pages, const PageMap& pm, int H, int R, const float* sink,
-                                         const RowMeta& rm, float* out, int M, cudaStream_t st) {
-    if (!latent_attention_rows_supported(H, R)) return cudaErrorNotSupported;
-    const size_t smem = ((size_t)R + (size_t)kLatentWarps * (R + 2)) * 4;
+                                         const RowMeta& rm, float* out, int M, cudaStream_t st, int key_extra, int window) {
+    const int RK = R + key_extra;
+    if (!latent_attention_rows_supported(H, RK)) return cudaErrorNotSupported;
+    const size_t smem = ((size_t)RK + (size_t)kLatentWarps * (R + 2)) * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(latent_attention_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
     return launch_pdl(latent_attention_rows_kernel, dim3(M, H), dim3(kLatentWarps * 32), smem, st, q, pages, pm.table, pm.max_pages,
-                      pm.page_size, H, R, sink, rm.slot, rm.pos, out);
+                      pm.page_size, H, R, RK, window, sink, rm.slot, rm.pos, out);
 }
 
 cudaError_t launch_head_linear(const float* A, int lda, const void* W, float* Y, int ldy, void* y_bf16, int M, int H, int N, int K,
-                               float alpha, const float* gate, int ldg, cudaStream_t st) {
+                               float alpha, const float* gate, int ldg, cudaStream_t st, int a_hs, int y_hs) {
     const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(W);
     __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y_bf16);
+    if (a_hs <= 0) a_hs = K;                                  // heads adjacent in A and in Y unless strides are given
+    if (y_hs <= 0) y_hs = N;
     if (M <= kRowsKernelMax)
         return launch_pdl(head_linear_rows_kernel, dim3((H * N + 7) / 8, M), dim3(256), 0, st, A, lda, w, Y, ldy, yb, H, N, K, alpha,
-                          gate, ldg);
+                          gate, ldg, a_hs, y_hs);
     if (H > 65535) return cudaErrorNotSupported;
     head_linear_tile_kernel<<<dim3((N + HB - 1) / HB, (M + HB - 1) / HB, H), 256, 0, st>>>(A, lda, w, Y, ldy, yb, M, N, K, alpha, gate,
-                                                                                          ldg);
+                                                                                          ldg, a_hs, y_hs);
     return cudaGetLastError();
 }
 

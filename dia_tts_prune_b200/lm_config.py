@@ -1,5 +1,5 @@
-"""Configuration schemas of the decoder-only language models (``config.json`` of a model folder): Pubopel, Kupelix and
-Luketar.
+"""Configuration schemas of the decoder-only language models (``config.json`` of a model folder): Pubopel, Kupelix,
+Luketar and Fipadra.
 
 Every size and every per-model constant comes from the file.  Optional entries that are absent switch their
 mechanism off: no ``mask`` is full causal attention, no ``softcap`` leaves scores uncapped, ``mlp: null`` is a layer
@@ -281,7 +281,122 @@ class LuketarConfig(BaseModel, frozen=True):
                 raise ValueError(f"layer {i}: top ({f.router.top}) exceeds experts ({f.router.experts})")
 
 
-CONFIGS = {"pubopel": PubopelConfig, "kupelix": KupelixConfig, "luketar": LuketarConfig}
+# ---- Fipadra: parallel layers with two RMS norms (x += mixer(norm1 x) + ff(norm2 x)); gated delta rule / latent attention with a
+# ---- turned key part and a sliding window / retention; squared-relu dense units or a grouped, softmax-scored mixture ----
+class GatedDeltaMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    kv_heads: Optional[int] = Field(default=None, gt=0)
+    dim: int = Field(gt=0)
+    vdim: int = Field(gt=0)
+    conv: int = Field(ge=1)                      # taps of the short convolutions of q, k, v
+
+
+class WindowConfig(BaseModel, frozen=True):
+    size: int = Field(gt=0)                      # position i sees j when 0 <= i - j < size
+
+
+class RotaryLatentMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    dim: int = Field(gt=0)                       # query / key channels per head that do not turn
+    rot_dim: int = Field(default=0, ge=0)        # ... and that turn with the position (the key's are shared by all heads)
+    vdim: int = Field(gt=0)
+    q_rank: int = Field(gt=0)
+    kv_rank: int = Field(gt=0)
+    scale: float
+    rot: Optional[RotConfig] = None
+    mask: Optional[WindowConfig] = None
+
+
+class RetentionMixerConfig(BaseModel, frozen=True):
+    heads: int = Field(gt=0)
+    dim: int = Field(gt=0)
+    vdim: int = Field(gt=0)
+    decay: list[float]                           # one fixed decay per head
+    rot: Optional[RotConfig] = None
+
+
+class GroupConfig(BaseModel, frozen=True):
+    count: int = Field(ge=1)                     # equal groups of neighbouring router outputs
+    keep: int = Field(ge=1)                      # groups a token may choose from
+
+
+class GroupedRouterConfig(BaseModel, frozen=True):
+    experts: int = Field(gt=0)
+    top: int = Field(gt=0)
+    identity: int = Field(default=0, ge=0)       # router outputs behind the experts' whose expert returns its input
+    scale: float = 1.0
+    groups: Optional[GroupConfig] = None
+
+
+class GroupedMoeMlpConfig(BaseModel, frozen=True):
+    kind: Literal["moe"]
+    expert: GatedUnitConfig
+    router: GroupedRouterConfig
+    shared: Optional[GatedUnitConfig] = None
+
+
+FipadraMlp = Annotated[Union[DenseMlpConfig, GroupedMoeMlpConfig], Field(discriminator="kind")]
+
+
+class FipadraDeltaLayer(BaseModel, frozen=True):
+    type: Literal["delta"]
+    mixer: GatedDeltaMixerConfig
+    mlp: Optional[FipadraMlp] = None
+
+
+class FipadraAttentionLayer(BaseModel, frozen=True):
+    type: Literal["latent_attention"]
+    mixer: RotaryLatentMixerConfig
+    mlp: Optional[FipadraMlp] = None
+
+
+class FipadraRetentionLayer(BaseModel, frozen=True):
+    type: Literal["retention"]
+    mixer: RetentionMixerConfig
+    mlp: Optional[FipadraMlp] = None
+
+
+FipadraLayer = Annotated[Union[FipadraDeltaLayer, FipadraAttentionLayer, FipadraRetentionLayer], Field(discriminator="type")]
+
+
+class FipadraConfig(BaseModel, frozen=True):
+    architecture: Literal["Fipadra"] = "Fipadra"
+    vocab: int = Field(gt=0)
+    width: int = Field(gt=0)
+    layers: list[FipadraLayer] = Field(min_length=1)
+    norm: NormConfig
+    logit_scale: float = 1.0
+
+    @classmethod
+    def load(cls, path: str | Path) -> "FipadraConfig":
+        return cls.model_validate(json.loads(Path(path).read_text(encoding="utf-8")))
+
+    def check(self) -> None:
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            g = getattr(m, "kv_heads", None) or m.heads
+            if m.heads % g:
+                raise ValueError(f"layer {i}: heads ({m.heads}) must be a multiple of kv_heads ({g})")
+            rot = getattr(m, "rot", None)
+            if rot is not None:
+                turning = m.rot_dim if layer.type == "latent_attention" else m.dim
+                if rot.dims % 2 or rot.dims > turning:
+                    raise ValueError(f"layer {i}: rot.dims ({rot.dims}) must be even and at most {turning}")
+            if layer.type == "retention" and len(m.decay) != m.heads:
+                raise ValueError(f"layer {i}: decay needs one number per head")
+            f = layer.mlp
+            if f is not None and f.kind == "moe":
+                n = f.router.experts + f.router.identity
+                per = n
+                if f.router.groups is not None:
+                    if n % f.router.groups.count or f.router.groups.keep > f.router.groups.count:
+                        raise ValueError(f"layer {i}: {n} router outputs do not form {f.router.groups.count} equal groups")
+                    per = f.router.groups.keep * (n // f.router.groups.count)
+                if f.router.top > per:
+                    raise ValueError(f"layer {i}: top ({f.router.top}) exceeds the router outputs a token may choose from ({per})")
+
+
+CONFIGS = {"pubopel": PubopelConfig, "kupelix": KupelixConfig, "luketar": LuketarConfig, "fipadra": FipadraConfig}
 
 
 def load_config(raw: dict):

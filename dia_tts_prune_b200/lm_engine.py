@@ -13,7 +13,7 @@ import numpy as np
 import torch
 
 from . import _lm_lib
-from .lm_layers import DynamicTanh, LayerNorm, MixLayer
+from .lm_layers import DynamicTanh, LayerNorm, MixLayer, RmsNorm
 from .lm_state import PagedState, Sequence
 
 
@@ -26,9 +26,10 @@ def launch_count() -> int:
 
 
 class LMEngine:
-    def __init__(self, layers: list, embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh | LayerNorm, *,
+    def __init__(self, layers: list, embed: torch.Tensor, head: torch.Tensor, final_norm: DynamicTanh | LayerNorm | RmsNorm, *,
                  width: int, vocab: int, taps: int, eps: float, state: PagedState, max_rows: int = 1024,
-                 precision: str = "bfloat16", step_graphs: bool = True, logit_scale: float = 1.0, embed_scale: float = 1.0):
+                 precision: str = "bfloat16", step_graphs: bool = True, logit_scale: float = 1.0, embed_scale: float = 1.0,
+                 embed_norm: torch.Tensor | None = None):
         """``layers``: the layer records in execution order (a layer that runs twice per token appears twice, each time
         with the state record of its own index)."""
         if not torch.cuda.is_available():
@@ -58,6 +59,9 @@ class LMEngine:
         m.step_graphs = 1 if step_graphs else 0
         m.logit_scale = float(logit_scale)
         m.embed_scale = float(embed_scale)
+        # an RMS norm weight on the embedding rows (stream records only)
+        self.embed_norm = None if embed_norm is None else embed_norm.detach().to(device=self.device, dtype=torch.float32).contiguous()
+        m.embed_norm = self.embed_norm.data_ptr() if self.embed_norm is not None else None
         recs = (_lm_lib.Layer * len(layers))()
         for i, layer in enumerate(layers):
             layer.fill(recs[i], state.record_state(i))

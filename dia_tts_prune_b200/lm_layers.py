@@ -23,10 +23,23 @@ Beside ``layers.py`` (Dia's RMSNorm / rotary attention / gated MLP modules) this
   * :class:`MLstm` - matrix memory with an exponential input gate, capped gate pre-activations, a running maximum that
     keeps the exponentials in range and a normaliser state;
   * :class:`GatedUnit` - gate / up / down unit with the clamped activation ``g' sigmoid(1.702 g') (u' + 1)``; the same
-    activation, a logit bias and softmax-over-the-chosen output weights are options of :class:`RoutedExperts`.
+    activation, a logit bias and softmax-over-the-chosen output weights are options of :class:`RoutedExperts`;
+  * :class:`RmsNorm` - ``x / sqrt(mean(x^2) + eps) w``, as a sublayer norm of the stream form, the final norm and the
+    norm of the embedding output;
+  * :class:`GatedDelta` - gated delta rule with ONE decay per head and token (single-step decay and gate projections, a
+    silu output gate), beside :class:`ChannelDelta`;
+  * :class:`Retention` - linear attention with a fixed decay per head, rotary q and k ("half" pairs), no softmax and no
+    denominator;
+  * options of :class:`LatentAttention`: a turned key part shared by all heads behind the cached latent (the query heads
+    carry a turned part of their own), a sliding window, no sink, no gate;
+  * :class:`DenseRelu2` - up projection, squared relu, down projection;
+  * options of :class:`RoutedExperts`: scores from the softmax over ALL router outputs, a correction that only the choice
+    sees, choice inside the best groups of neighbouring outputs, normalised and scaled weights, identity experts, a
+    sigmoid gate number on the shared unit.
 All constants are constructor arguments; a design picks and combines them per layer (:class:`MixLayer` runs its
 sublayers one after the other, :class:`ParallelLayer` feeds one norm to mixer and feed-forward and adds both,
-:class:`StreamLayer` runs pre-norm sublayers over hyper-connected streams).  The arithmetic lives in
+:class:`StreamLayer` runs pre-norm sublayers over hyper-connected streams - with ``parallel`` both sublayers read the
+streams before either writes).  The arithmetic lives in
 ``csrc/lm_kernels.cu``, ``csrc/lm_mixers.cu`` and ``csrc/lm_streams.cu``; these classes only keep device tensors alive
 and fill ``lm_b200_layer``.
 """
@@ -82,15 +95,31 @@ class SinkAttention:
 
 class RoutedExperts:
     def __init__(self, router, gates: list, ups: list, downs: list, *, top: int, shared=None, device=None,
-                 router_bias=None, softmax_top: bool = False, limit: float | None = None, shared_limit: float | None = None):
+                 router_bias=None, softmax_top: bool = False, limit: float | None = None, shared_limit: float | None = None,
+                 softmax_all: bool = False, identity: int = 0, correction=None, groups: tuple[int, int] | None = None,
+                 route_scale: float = 1.0, shared_gate=None):
         """``gates[e] / ups[e]: [ff, width]``, ``downs[e]: [width, ff]``; ``shared``: (gate, up, down) or None.
         ``softmax_top``: the softmax over the chosen logits weighs the experts' OUTPUTS (otherwise sigmoid scores scale
-        their inputs); ``limit`` / ``shared_limit``: the clamped activation instead of silu(g) u."""
+        their inputs); ``limit`` / ``shared_limit``: the clamped activation instead of silu(g) u.
+        ``softmax_all``: scores are the softmax over all router outputs; the choice is made on score + ``correction``,
+        inside the ``groups = (count, keep)`` best groups of neighbouring outputs; the chosen scores, divided by their sum and
+        times ``route_scale``, weigh the outputs.  The last ``identity`` router outputs have no weights: their expert
+        returns its input.  ``shared_gate [1, width]``: the shared unit's output is times sigmoid(shared_gate . h)."""
         self.router_bias = None if router_bias is None else _f32(router_bias, device)
-        self.softmax_top = bool(softmax_top)
+        self.softmax_top, self.softmax_all = bool(softmax_top), bool(softmax_all)
+        self.identity, self.route_scale = int(identity), float(route_scale)
+        self.groups = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+        self.correction = None if correction is None else _f32(correction, device)
         self.limit = None if limit is None else float(limit)
         self.shared_limit = float(shared_limit) if shared_limit is not None else self.limit
         self.experts, self.top, self.ff = len(gates), int(top), int(gates[0].shape[0])
+        if tuple(router.shape)[0] != self.experts + self.identity:
+            raise ValueError("the router needs one row per expert and identity expert")
+        self.has_shared_gate = shared_gate is not None
+        if self.has_shared_gate:                                  # the gate's row rides behind the router's: one product
+            if shared is None or not softmax_all:
+                raise ValueError("a shared gate needs a shared unit and the softmax-over-all router")
+            router = torch.cat([router, shared_gate.reshape(1, -1)], dim=0)
         self.w_router = _bf16(router, device)
         self.w_gate_up = _bf16(torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]), device)
         self.w_down = _bf16(torch.stack(list(downs)), device)
@@ -369,13 +398,23 @@ class LatentAttention:
     kind = "latent_attention"
 
     def __init__(self, w_dq, q_lat_norm, w_uq, w_dkv, kv_lat_norm, w_uk, w_uv, w_gate, w_o, *, heads: int, dim: int, vdim: int,
-                 scale: float, sink=None, device=None):
+                 scale: float, sink=None, device=None, rot_dim: int = 0, rot_angles=None, rot_half: bool = False,
+                 window: int | None = None):
+        """``rot_dim`` > 0: every query head is ``[dim plain | rot_dim turned]`` (``w_uq`` has heads x (dim + rot_dim) rows) and
+        ``w_dkv`` has ``rot_dim`` more rows behind the latent's: one turned key part for all heads, cached beside the
+        latent.  ``rot_angles``: angle per position of the turning pairs (the first 2 x len channels of the turned part).
+        ``window``: a position sees itself and the ``window - 1`` before it.  ``w_gate`` None: no output gate."""
         self.heads, self.dim, self.vdim, self.scale = int(heads), int(dim), int(vdim), float(scale)
-        self.q_rank, self.kv_rank = int(w_dq.shape[0]), int(w_dkv.shape[0])
-        if (tuple(w_uq.shape) != (heads * dim, self.q_rank) or tuple(w_uk.shape) != (heads * dim, self.kv_rank)
-                or tuple(w_uv.shape) != (heads * vdim, self.kv_rank) or tuple(w_gate.shape)[0] != heads * vdim):
+        self.rot_dim, self.rot_half, self.window = int(rot_dim), bool(rot_half), int(window) if window else 0
+        self.q_rank, self.kv_rank = int(w_dq.shape[0]), int(w_dkv.shape[0]) - self.rot_dim
+        if (tuple(w_uq.shape) != (heads * (dim + self.rot_dim), self.q_rank) or tuple(w_uk.shape) != (heads * dim, self.kv_rank)
+                or tuple(w_uv.shape) != (heads * vdim, self.kv_rank) or (w_gate is not None and tuple(w_gate.shape)[0] != heads * vdim)):
             raise ValueError("projection shapes do not match heads x dim and the latent sizes")
-        self.in_rows, self.in_bias, self.w_o = [w_dq, w_dkv, w_gate], None, w_o
+        self.gated = w_gate is not None
+        self.in_rows, self.in_bias, self.w_o = [w_dq, w_dkv] + ([w_gate] if self.gated else []), None, w_o
+        self.rot = None if rot_angles is None or rot_angles.numel() == 0 else _f32(rot_angles, device)
+        if self.rot is not None and 2 * self.rot.numel() > self.rot_dim:
+            raise ValueError("more turning channels than the turned part has")
         self.q_lat_norm, self.kv_lat_norm = _f32(q_lat_norm, device), _f32(kv_lat_norm, device)
         self.w_uq = _bf16(w_uq, device)
         # scores are taken in the latent space: q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, so the kernels want W_uk,h^T
@@ -384,11 +423,16 @@ class LatentAttention:
         self.sink = None if sink is None else _f32(sink, device)
 
     def state_spec(self) -> StateSpec:
-        return StateSpec(latent=self.kv_rank)
+        return StateSpec(latent=self.kv_rank + self.rot_dim)
 
     def fill(self, rec, st) -> None:
-        from ._lm_lib import MIXER_LATENT_ATTENTION
+        from ._lm_lib import GATE_NONE, GATE_SIGMOID, MIXER_LATENT_ATTENTION, ROT_HALF, ROT_INTERLEAVED
         rec.mixer = MIXER_LATENT_ATTENTION
+        rec.mixer_gate = GATE_SIGMOID if self.gated else GATE_NONE
+        rec.rot_dim, rec.window = self.rot_dim, self.window
+        rec.rot_dims = 2 * self.rot.numel() if self.rot is not None else 0
+        rec.rot_freq = self.rot.data_ptr() if self.rot is not None else None
+        rec.rot_layout = ROT_HALF if self.rot_half else ROT_INTERLEAVED
         rec.heads, rec.kv_heads, rec.dim, rec.vdim, rec.scale = self.heads, 1, self.dim, self.vdim, self.scale
         rec.q_rank, rec.kv_rank = self.q_rank, self.kv_rank
         rec.q_lat_norm, rec.kv_lat_norm = self.q_lat_norm.data_ptr(), self.kv_lat_norm.data_ptr()
@@ -426,6 +470,95 @@ class MLstm:
         rec.rec_state, rec.rec_aux = st.rec_state.data_ptr(), st.rec_aux.data_ptr()
 
 
+def _gate_kind(gate: str | None) -> int:
+    from ._lm_lib import GATE_NONE, GATE_SIGMOID, GATE_SILU
+    return {None: GATE_NONE, "sigmoid": GATE_SIGMOID, "silu": GATE_SILU}[gate]
+
+
+class GatedDelta:
+    kind = "gated_delta"
+
+    def __init__(self, w_q, w_k, w_v, w_beta, w_a, w_gate, w_o, conv_q, conv_k, conv_v, a_log, dt_bias, head_norm, *, heads: int,
+                 kv_heads: int, dim: int, vdim: int, unit_eps: float = 1e-6, gate: str | None = "silu", device=None):
+        """Per head S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q with ONE decay g = exp(-exp(a_log) softplus(w_a . h
+        + dt_bias)) per head and token; q, k, v pass a short causal convolution and silu, q and k become unit vectors (q
+        also x dim^-1/2); o / rms(o) x head_norm [vdim] x gate(w_gate h)."""
+        self.heads, self.kv_heads, self.dim, self.vdim = int(heads), int(kv_heads), int(dim), int(vdim)
+        if (tuple(w_q.shape)[0] != kv_heads * dim or tuple(w_k.shape)[0] != kv_heads * dim or tuple(w_v.shape)[0] != heads * vdim
+                or tuple(w_beta.shape)[0] != heads or tuple(w_a.shape)[0] != heads or heads % kv_heads):
+            raise ValueError("projection shapes do not match heads x dim")
+        self.taps, self.gate = int(conv_q.shape[1]), gate
+        self.in_rows = [w_q, w_k, w_v, w_beta, w_a] + ([w_gate] if gate is not None else [])
+        self.in_bias, self.w_o = None, w_o
+        self.conv_w = _f32(torch.cat([conv_q, conv_k, conv_v], dim=0), device)
+        self.a_log, self.dt_bias = _f32(a_log, device), _f32(dt_bias, device)
+        self.head_norm = _f32(head_norm, device)
+        self.unit_eps = float(unit_eps)
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec(recurrent=(self.heads, self.vdim, self.dim),
+                         conv=(self.taps, 2 * self.kv_heads * self.dim + self.heads * self.vdim))
+
+    def fill(self, rec, st) -> None:
+        from ._lm_lib import MIXER_GATED_DELTA
+        rec.mixer, rec.mixer_gate = MIXER_GATED_DELTA, _gate_kind(self.gate)
+        rec.heads, rec.kv_heads, rec.dim, rec.vdim = self.heads, self.kv_heads, self.dim, self.vdim
+        rec.conv_taps, rec.unit_eps = self.taps, self.unit_eps
+        rec.conv_w, rec.a_log, rec.dt_bias = self.conv_w.data_ptr(), self.a_log.data_ptr(), self.dt_bias.data_ptr()
+        rec.head_norm = self.head_norm.data_ptr()
+        rec.rec_state, rec.conv_tail = st.rec_state.data_ptr(), st.conv_tail.data_ptr()
+
+
+class Retention:
+    kind = "retention"
+
+    def __init__(self, w_q, w_k, w_v, w_gate, w_o, decay, *, heads: int, dim: int, vdim: int, rot_angles=None, rot_half: bool = True,
+                 head_norm=None, gate: str | None = "silu", device=None):
+        """Per head S_t = decay S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with a fixed ``decay`` per head; q and k turn with the
+        position (``rot_angles`` per pair), k also x dim^-1/2; o / rms(o) per head (x ``head_norm [vdim]`` if given) x
+        gate(w_gate h)."""
+        self.heads, self.dim, self.vdim = int(heads), int(dim), int(vdim)
+        if (tuple(w_q.shape)[0] != heads * dim or tuple(w_k.shape)[0] != heads * dim or tuple(w_v.shape)[0] != heads * vdim
+                or len(decay) != heads):
+            raise ValueError("projection shapes do not match heads x dim")
+        self.gate, self.rot_half = gate, bool(rot_half)
+        self.in_rows = [w_q, w_k, w_v] + ([w_gate] if gate is not None else [])
+        self.in_bias, self.w_o = None, w_o
+        self.decay = _f32(torch.tensor([float(d) for d in decay], dtype=torch.float64), device)
+        self.rot = None if rot_angles is None or rot_angles.numel() == 0 else _f32(rot_angles, device)
+        self.head_norm = None if head_norm is None else _f32(head_norm, device)
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec(recurrent=(self.heads, self.vdim, self.dim))
+
+    def fill(self, rec, st) -> None:
+        from ._lm_lib import MIXER_RETENTION, ROT_HALF, ROT_INTERLEAVED
+        rec.mixer, rec.mixer_gate = MIXER_RETENTION, _gate_kind(self.gate)
+        rec.heads, rec.kv_heads, rec.dim, rec.vdim = self.heads, self.heads, self.dim, self.vdim
+        rec.head_decay = self.decay.data_ptr()
+        rec.head_norm = self.head_norm.data_ptr() if self.head_norm is not None else None
+        rec.rot_dims = 2 * self.rot.numel() if self.rot is not None else 0
+        rec.rot_freq = self.rot.data_ptr() if self.rot is not None else None
+        rec.rot_layout = ROT_HALF if self.rot_half else ROT_INTERLEAVED
+        rec.rec_state = st.rec_state.data_ptr()
+
+
+class DenseRelu2:
+    def __init__(self, w_up, w_down, device=None):
+        """``down(max(up h, 0)^2)``."""
+        self.ff = int(w_up.shape[0])
+        self.w_up, self.w_down = _bf16(w_up, device), _bf16(w_down, device)
+
+
+class RmsNorm:
+    def __init__(self, weight: torch.Tensor, device):
+        self.w = _f32(weight, device)
+
+    def fill(self, rec) -> None:
+        from ._lm_lib import NORM_RMS
+        rec.w, rec.b, rec.alpha, rec.kind = self.w.data_ptr(), None, 0.0, NORM_RMS
+
+
 class GatedUnit:
     def __init__(self, w_gate, w_up, w_down, *, limit: float | None, device=None):
         """``down(act(gate h, up h))``; with ``limit`` the clamped activation, without it silu(g) u."""
@@ -439,8 +572,12 @@ class StreamLayer:
     reads the mixer's input is one stacked matrix.  The same object may stand in several layer records (a layer that runs
     with another layer's weights): each record gets a state of its own."""
 
-    def __init__(self, norm1, hc1: HyperConnection, mixer, ff=None, norm2=None, hc2: HyperConnection | None = None, device=None):
+    def __init__(self, norm1, hc1: HyperConnection, mixer, ff=None, norm2=None, hc2: HyperConnection | None = None, device=None,
+                 parallel: bool = False, rms: bool = False):
+        """``parallel``: the feed-forward reads the streams as they were before the mixer's write, and both outputs are
+        written at once (with one stream: x += mixer(norm1 x) + ff(norm2 x)).  ``rms``: the norms are RMS norms."""
         self.mixer, self.ff, self.hc1, self.hc2 = mixer, ff, hc1, hc2
+        self.parallel, self.rms = bool(parallel), bool(rms)
         self.norm1 = _f32(norm1, device)
         self.norm2 = None if norm2 is None else _f32(norm2, device)
         if ff is not None and (norm2 is None or hc2 is None or hc2.streams != hc1.streams):
@@ -461,10 +598,11 @@ class StreamLayer:
         return self.mixer.state_spec()
 
     def fill(self, rec, st) -> None:
-        from ._lm_lib import (ACT_CLAMPED_GLU, ACT_SILU_GLU, FF_DENSE, FF_NONE, FF_ROUTED_EXPERTS, FORM_STREAMS, NORM_LAYER,
-                              ROUTER_SIGMOID_INPUT, ROUTER_SOFTMAX_TOP)
-        rec.form, rec.streams = FORM_STREAMS, self.hc1.streams
-        rec.norm_mix_in.w, rec.norm_mix_in.b, rec.norm_mix_in.kind = self.norm1.data_ptr(), None, NORM_LAYER
+        from ._lm_lib import (ACT_CLAMPED_GLU, ACT_RELU2, ACT_SILU_GLU, FF_DENSE, FF_NONE, FF_ROUTED_EXPERTS, FORM_STREAMS,
+                              NORM_LAYER, NORM_RMS, ROUTER_SIGMOID_INPUT, ROUTER_SOFTMAX_GROUPED, ROUTER_SOFTMAX_TOP)
+        norm_kind = NORM_RMS if self.rms else NORM_LAYER
+        rec.form, rec.streams, rec.parallel = FORM_STREAMS, self.hc1.streams, 1 if self.parallel else 0
+        rec.norm_mix_in.w, rec.norm_mix_in.b, rec.norm_mix_in.kind = self.norm1.data_ptr(), None, norm_kind
         for q, hc in enumerate((self.hc1, self.hc2)):
             if hc is not None:
                 rec.hc_in[q], rec.hc_out[q], rec.hc_mix[q] = hc.w_in.data_ptr(), hc.w_out.data_ptr(), hc.w_mix.data_ptr()
@@ -475,7 +613,11 @@ class StreamLayer:
         f = self.ff
         if f is None:
             return
-        rec.norm_ff_in.w, rec.norm_ff_in.b, rec.norm_ff_in.kind = self.norm2.data_ptr(), None, NORM_LAYER
+        rec.norm_ff_in.w, rec.norm_ff_in.b, rec.norm_ff_in.kind = self.norm2.data_ptr(), None, norm_kind
+        if isinstance(f, DenseRelu2):
+            rec.ff, rec.dense_ff, rec.act = FF_DENSE, f.ff, ACT_RELU2
+            rec.ws_gate_up, rec.ws_down = f.w_up.data_ptr(), f.w_down.data_ptr()
+            return
         rec.act = ACT_CLAMPED_GLU if f.limit is not None else ACT_SILU_GLU
         rec.act_limit = f.limit if f.limit is not None else 0.0
         if isinstance(f, GatedUnit):
@@ -484,7 +626,10 @@ class StreamLayer:
             return
         rec.ff = FF_ROUTED_EXPERTS
         rec.experts, rec.top, rec.expert_ff, rec.shared_ff = f.experts, f.top, f.ff, f.shared_ff
-        rec.router = ROUTER_SOFTMAX_TOP if f.softmax_top else ROUTER_SIGMOID_INPUT
+        rec.router = ROUTER_SOFTMAX_GROUPED if f.softmax_all else ROUTER_SOFTMAX_TOP if f.softmax_top else ROUTER_SIGMOID_INPUT
+        rec.identity_experts, rec.route_scale, rec.shared_gate = f.identity, f.route_scale, 1 if f.has_shared_gate else 0
+        rec.group_count, rec.group_keep = f.groups
+        rec.route_correction = f.correction.data_ptr() if f.correction is not None else None
         rec.router_bias = f.router_bias.data_ptr() if f.router_bias is not None else None
         rec.shared_limit = f.shared_limit if f.shared_limit is not None else 0.0
         rec.w_router, rec.w_gate_up, rec.w_down = f.w_router.data_ptr(), f.w_gate_up.data_ptr(), f.w_down.data_ptr()

@@ -18,11 +18,11 @@ from pathlib import Path
 import torch
 
 from .checkpoint import load_safetensors
-from .lm_config import KupelixConfig, LuketarConfig, PubopelConfig, load_config
+from .lm_config import FipadraConfig, KupelixConfig, LuketarConfig, PubopelConfig, load_config
 from .lm_engine import LMEngine
-from .lm_layers import (ChannelDelta, DenseXielu, DynamicTanh, GatedUnit, Hgrn2, HyperConnection, LatentAttention, LayerNorm,
-                        LayerRun, MixLayer, MLstm, ParallelLayer, RoutedExperts, SinkAttention, StreamLayer, TalkingAttention,
-                        TapMix, rotary_angles)
+from .lm_layers import (ChannelDelta, DenseRelu2, DenseXielu, DynamicTanh, GatedDelta, GatedUnit, Hgrn2, HyperConnection,
+                        LatentAttention, LayerNorm, LayerRun, MixLayer, MLstm, ParallelLayer, Retention, RmsNorm, RoutedExperts,
+                        SinkAttention, StreamLayer, TalkingAttention, TapMix, rotary_angles)
 from .lm_state import OutOfPages, PagedState, Sequence
 
 
@@ -134,6 +134,47 @@ def build_luketar_layers(cfg: LuketarConfig, w: dict[str, torch.Tensor], device)
     return runs, LayerNorm(w["final.norm"], None, device)
 
 
+def build_fipadra_layers(cfg: FipadraConfig, w: dict[str, torch.Tensor], device) -> tuple[list[StreamLayer], RmsNorm]:
+    """The layer records of a Fipadra checkpoint (tensor names ``l<i>.norm1``, ``l<i>.norm2``, ``l<i>.mix.*``,
+    ``l<i>.mlp.*``): stream records with one plain residual stream, RMS norms, and both sublayers reading the same x."""
+    residual = HyperConnection.residual(device)                   # one object: both sublayers read with the same weights
+    layers = []
+    for i, lc in enumerate(cfg.layers):
+        p, m = f"l{i}.mix.", lc.mixer
+        t = lambda name: w[p + name]                             # noqa: E731
+        rot = getattr(m, "rot", None)
+        angles = rotary_angles(rot.base, rot.dims, rot.scaling) if rot is not None and rot.dims > 0 else None
+        if lc.type == "delta":
+            mixer = GatedDelta(t("q"), t("k"), t("v"), t("b"), t("a"), t("g"), t("o"), t("q.conv"), t("k.conv"), t("v.conv"),
+                               t("A_log"), t("dt_bias"), t("norm"), heads=m.heads, kv_heads=m.kv_heads or m.heads, dim=m.dim,
+                               vdim=m.vdim, gate="silu", device=device)
+        elif lc.type == "latent_attention":
+            mixer = LatentAttention(t("dq"), t("dq.norm"), t("uq"), t("dkv"), t("dkv.norm"), t("uk"), t("uv"), None, t("o"),
+                                    heads=m.heads, dim=m.dim, vdim=m.vdim, scale=m.scale, sink=None, rot_dim=m.rot_dim,
+                                    rot_angles=angles, rot_half=False, window=m.mask.size if m.mask else None, device=device)
+        else:
+            mixer = Retention(t("q"), t("k"), t("v"), t("g"), t("o"), m.decay, heads=m.heads, dim=m.dim, vdim=m.vdim,
+                              rot_angles=angles, rot_half=True, head_norm=None, gate="silu", device=device)
+        ff = norm2 = None
+        f, q = lc.mlp, f"l{i}.mlp."
+        if f is not None:
+            norm2 = w[f"l{i}.norm2"]
+            if f.kind == "dense":
+                ff = DenseRelu2(w[q + "up"], w[q + "down"], device=device)
+            else:
+                E, r = f.router.experts, f.router
+                shared = (w[q + "shared.gate"], w[q + "shared.up"], w[q + "shared.down"]) if f.shared is not None else None
+                ff = RoutedExperts(w[q + "router"], [w[q + f"e{e}.gate"] for e in range(E)], [w[q + f"e{e}.up"] for e in range(E)],
+                                   [w[q + f"e{e}.down"] for e in range(E)], top=r.top, shared=shared, device=device,
+                                   limit=f.expert.limit, shared_limit=f.shared.limit if f.shared is not None else None,
+                                   softmax_all=True, identity=r.identity, correction=w.get(q + "correction"),
+                                   groups=(r.groups.count, r.groups.keep) if r.groups is not None else None, route_scale=r.scale,
+                                   shared_gate=w[q + "shared.sg"] if f.shared is not None else None)
+        layers.append(StreamLayer(w[f"l{i}.norm1"], residual, mixer, ff, norm2, residual if ff is not None else None, device=device,
+                                  parallel=True, rms=True))
+    return layers, RmsNorm(w["final.norm"], device)
+
+
 @dataclass
 class Request:
     name: str
@@ -220,7 +261,7 @@ class Scheduler:
 
 
 class CausalLM:
-    def __init__(self, cfg: PubopelConfig | KupelixConfig | LuketarConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
+    def __init__(self, cfg: PubopelConfig | KupelixConfig | LuketarConfig | FipadraConfig, weights: dict[str, torch.Tensor], dtype: str = "bfloat16", device=None,
                  max_tokens: int = 4096, max_sequences: int = 8, page_size: int = 16, max_rows: int = 1024,
                  max_sequence_tokens: int | None = None, step_graphs: bool = True):
         if dtype not in ("bfloat16", "float32"):
@@ -231,8 +272,12 @@ class CausalLM:
         self.config, self.dtype = cfg, dtype
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         # a design is its layer records (in execution order), its final norm and the constants around them
-        embed_scale, head = 1.0, weights.get("head")
-        if isinstance(cfg, KupelixConfig):
+        embed_scale, head, embed_norm = 1.0, weights.get("head"), None
+        if isinstance(cfg, FipadraConfig):
+            self.layers, final_norm = build_fipadra_layers(cfg, weights, self.device)
+            taps, logit_scale = 0, cfg.logit_scale
+            head, embed_norm = weights["embed"], weights["embed.norm"]    # logits against the table itself; a norm behind the lookup
+        elif isinstance(cfg, KupelixConfig):
             self.layers, final_norm = build_kupelix_layers(cfg, weights, self.device)
             taps, logit_scale = 0, cfg.logit_scale
         elif isinstance(cfg, LuketarConfig):
@@ -249,7 +294,7 @@ class CausalLM:
         # pages, recurrent states and the residual stream are float32 in both.
         self.engine = LMEngine(self.layers, weights["embed"], head, final_norm, width=cfg.width, vocab=cfg.vocab,
                                taps=taps, eps=cfg.norm.eps, state=self.state, max_rows=max_rows, precision=dtype,
-                               step_graphs=step_graphs, logit_scale=logit_scale, embed_scale=embed_scale)
+                               step_graphs=step_graphs, logit_scale=logit_scale, embed_scale=embed_scale, embed_norm=embed_norm)
         self._draws = 0
 
     @classmethod

@@ -55,6 +55,7 @@ def _ensure_builtin() -> None:
     register("Pubopel", _load_causal_lm)
     register("Kupelix", _load_causal_lm)
     register("Luketar", _load_causal_lm)
+    register("Fipadra", _load_causal_lm)
 
 
 def load_model(folder: str | Path, dtype: str = "bfloat16", device=None, **kw):

@@ -292,3 +292,92 @@ def luketar_weights(cfg: dict, seed: int = 1234, device="cpu") -> dict:
                 w[p + f"hc{q}.in"], w[p + f"hc{q}.out"] = vec(s, 1.0 / s, 0.05), vec(s, 1.0, 0.1)
                 w[p + f"hc{q}.mix"] = (torch.eye(s, device=device) + 0.1 * torch.randn((s, s), generator=g, device=device)).to(torch.bfloat16)
     return w
+
+
+def fipadra_config(width: int, kinds: list[str], heads: int, dim: int, vdim: int, vocab: int, kv_heads: int = 0, q_rank: int = 0,
+                   kv_rank: int = 0, rot_dim: int = 0, window: int = 0, taps: int = 4, ff: int = 0, experts: int = 0, top: int = 0,
+                   identity: int = 0, groups: tuple[int, int] | None = None, expert_ff: int = 0, shared_ff: int = 0,
+                   logit_scale: float = 1.0) -> dict:
+    """A Fipadra ``config.json`` as a dictionary: one layer per entry of ``kinds`` (``delta`` / ``latent_attention`` /
+    ``retention``); even layers get a dense unit of ``ff`` hidden units, odd ones ``experts`` routed units with ``identity``
+    identity experts (a dense unit when ``experts`` is 0)."""
+    layers = []
+    for n, kind in enumerate(kinds):
+        m = {"heads": heads, "dim": dim, "vdim": vdim}
+        if kind == "delta":
+            m.update(kv_heads=kv_heads or heads, conv=taps)
+        elif kind == "latent_attention":
+            m.update(q_rank=q_rank, kv_rank=kv_rank, rot_dim=rot_dim, scale=(dim + rot_dim) ** -0.5,
+                     rot={"base": 10000.0, "dims": rot_dim})
+            if window:
+                m["mask"] = {"size": window}
+        else:
+            m.update(decay=[1.0 - 2.0 ** (-5.0 - 6.0 * h / max(heads - 1, 1)) for h in range(heads)],
+                     rot={"base": 10000.0, "dims": dim})
+        if experts and n % 2 == 1:
+            router = {"experts": experts, "top": top, "identity": identity, "scale": 1.5}
+            if groups:
+                router["groups"] = {"count": groups[0], "keep": groups[1]}
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": router,
+                   "shared": {"ff": shared_ff, "limit": 7.0} if shared_ff else None}
+        else:
+            mlp = {"kind": "dense", "ff": ff} if ff else None
+        layers.append({"type": kind, "mixer": m, "mlp": mlp})
+    return {"architecture": "Fipadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": logit_scale,
+            "layers": layers}
+
+
+def fipadra_weights(cfg: dict, seed: int = 1234, device="cpu") -> dict:
+    """Random bfloat16 tensors under the checkpoint's names: matrices ~ N(0, 1 / fan_in), norm weights near one, decays of
+    the delta rule mostly close to one."""
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    D, V = cfg["width"], cfg["vocab"]
+
+    def mat(n, k, gain=1.0):
+        return (torch.randn((n, k), generator=g, device=device) * (gain * k ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, mean, spread):
+        return (mean + spread * torch.randn((n,), generator=g, device=device)).to(torch.bfloat16)
+
+    def unit(prefix, ff):
+        w[prefix + "gate"], w[prefix + "up"], w[prefix + "down"] = mat(ff, D), mat(ff, D), mat(D, ff)
+
+    w = {"embed": torch.randn((V, D), generator=g, device=device).to(torch.bfloat16), "embed.norm": vec(D, 1.0, 0.05),
+         "final.norm": vec(D, 1.0, 0.05)}
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lc["mixer"]
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        w[p + "norm1"] = vec(D, 1.0, 0.05)
+        if lc["type"] == "delta":
+            G, taps = m.get("kv_heads") or H, m["conv"]
+            for name, n in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                w[p + "mix." + name] = mat(n, D)
+                w[p + f"mix.{name}.conv"] = (torch.randn((n, taps), generator=g, device=device) * taps ** -0.5).to(torch.bfloat16)
+            w[p + "mix.b"], w[p + "mix.a"] = mat(H, D), mat(H, D)
+            w[p + "mix.A_log"], w[p + "mix.dt_bias"] = vec(H, -1.0, 0.5), vec(H, -2.0, 1.0)
+            w[p + "mix.norm"], w[p + "mix.g"] = vec(dv, 1.0, 0.05), mat(H * dv, D)
+        elif lc["type"] == "latent_attention":
+            rq, rk, dr = m["q_rank"], m["kv_rank"], m.get("rot_dim", 0)
+            w[p + "mix.dq"], w[p + "mix.dq.norm"], w[p + "mix.uq"] = mat(rq, D), vec(rq, 1.0, 0.05), mat(H * (d + dr), rq)
+            w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = mat(rk + dr, D), vec(rk, 1.0, 0.05)
+            w[p + "mix.uk"], w[p + "mix.uv"] = mat(H * d, rk), mat(H * dv, rk)
+        else:
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = mat(H * d, D), mat(H * d, D), mat(H * dv, D)
+            w[p + "mix.g"] = mat(H * dv, D)
+        w[p + "mix.o"] = mat(D, H * dv)
+        f = lc.get("mlp")
+        if f:
+            w[p + "norm2"] = vec(D, 1.0, 0.05)
+            if f["kind"] == "dense":
+                w[p + "mlp.up"], w[p + "mlp.down"] = mat(f["ff"], D), mat(D, f["ff"])
+            else:
+                r = f["router"]
+                n = r["experts"] + r.get("identity", 0)
+                for e in range(r["experts"]):
+                    unit(p + f"mlp.e{e}.", f["expert"]["ff"])
+                w[p + "mlp.router"], w[p + "mlp.correction"] = mat(n, D), vec(n, 0.0, 0.05)
+                if f.get("shared"):
+                    unit(p + "mlp.shared.", f["shared"]["ff"])
+                    w[p + "mlp.shared.sg"] = mat(1, D)
+    return w

@@ -10,6 +10,7 @@
  *   streams     s residual streams x_1 .. x_s (all equal to the embedding output at first, summed at the end); per sublayer
  *               u = sum_s in[s] x_s;  y = sublayer(norm(u));  x_j <- sum_s mix[s][j] x_s + out[j] y   (hyper-connections;
  *               s = 1 with unit weights is the plain pre-norm residual)
+ *               with `parallel`, both sublayers read the streams before either writes: x += mixer(norm1(x)) + ff(norm2(x))
  * and the mechanisms (norm kind, mixer kind, feed-forward kind) are selected and parameterised per record, so a design
  * combines them as it needs.  A layer that a design runs several times with the same weights is several records that
  * share weight pointers and differ in their state pointers.  Matrices are bf16 [out][in]; vectors and scalars fp32.
@@ -32,7 +33,7 @@
 extern "C" {
 #endif
 
-#define LM_B200_ABI_VERSION 3
+#define LM_B200_ABI_VERSION 4
 
 enum lm_b200_status { LM_B200_OK = 0, LM_B200_EINVAL = -1, LM_B200_ECUDA = -2, LM_B200_ENOMEM = -3, LM_B200_EUNSUPPORTED = -5 };
 
@@ -42,22 +43,34 @@ enum lm_b200_mixer_kind {
     LM_B200_MIXER_HGRN2 = 3,            /* gated linear recurrence: the forget gate also sets the write strength */
     LM_B200_MIXER_CHANNEL_DELTA = 4,    /* gated delta rule with a decay per head and key channel, short convolutions */
     LM_B200_MIXER_LATENT_ATTENTION = 5, /* queries through a normed latent, keys / values up-projected from one cached normed latent, sink, elementwise gate */
-    LM_B200_MIXER_MLSTM = 6             /* matrix memory with exponential input gate, running maximum and normaliser */
+    LM_B200_MIXER_MLSTM = 6,            /* matrix memory with exponential input gate, running maximum and normaliser */
+    LM_B200_MIXER_GATED_DELTA = 7,      /* gated delta rule with ONE decay per head and token, short convolutions, silu output gate */
+    LM_B200_MIXER_RETENTION = 8         /* linear attention with a fixed decay per head, rotary q / k, no softmax, no denominator */
 };
 enum lm_b200_ff_kind { LM_B200_FF_NONE = 0, LM_B200_FF_ROUTED_EXPERTS = 1, LM_B200_FF_DENSE = 2 };
-enum lm_b200_norm_kind { LM_B200_NORM_DYT = 0, LM_B200_NORM_LAYER = 1 };
+enum lm_b200_norm_kind { LM_B200_NORM_DYT = 0, LM_B200_NORM_LAYER = 1, LM_B200_NORM_RMS = 2 };
 enum lm_b200_layer_form { LM_B200_FORM_SEQUENTIAL = 0, LM_B200_FORM_PARALLEL = 1, LM_B200_FORM_STREAMS = 2 };
 /* XIELU: up, activation, down.  SILU_GLU / CLAMPED_GLU: gated units [gate | up] -> down with silu(g) u, or with
  * g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(1.702 g') (u' + 1) */
-enum lm_b200_act_kind { LM_B200_ACT_SILU_GLU = 0, LM_B200_ACT_XIELU = 1, LM_B200_ACT_CLAMPED_GLU = 2 };
+enum lm_b200_act_kind { LM_B200_ACT_SILU_GLU = 0, LM_B200_ACT_XIELU = 1, LM_B200_ACT_CLAMPED_GLU = 2,
+                        LM_B200_ACT_RELU2 = 3 /* dense, not gated: up, max(z, 0)^2, down */ };
 /* SIGMOID_INPUT: score sigmoid(z) multiplies the chosen expert's input.  SOFTMAX_TOP: the softmax over the chosen logits
  * alone weighs the experts' outputs */
-enum lm_b200_router_kind { LM_B200_ROUTER_SIGMOID_INPUT = 0, LM_B200_ROUTER_SOFTMAX_TOP = 1 };
+/* SOFTMAX_GROUPED: scores = softmax over ALL router outputs; the choice is made on score + correction, only inside the
+ * `group_keep` of `group_count` groups of neighbouring outputs whose largest choice score is largest; the chosen scores
+ * (without the correction), divided by their sum and times route_scale, weigh the experts' outputs.  The last
+ * `identity_experts` router outputs have no weights: their output is their input. */
+enum lm_b200_router_kind { LM_B200_ROUTER_SIGMOID_INPUT = 0, LM_B200_ROUTER_SOFTMAX_TOP = 1, LM_B200_ROUTER_SOFTMAX_GROUPED = 2 };
+/* what the columns `gate` of a mixer's stacked projections do to its output */
+enum lm_b200_gate_kind { LM_B200_GATE_SIGMOID = 0, LM_B200_GATE_NONE = 1, LM_B200_GATE_SILU = 2 };
+/* which channels of a head form a rotary pair: (2i, 2i + 1), or (i, i + rot_dims / 2) */
+enum lm_b200_rot_layout { LM_B200_ROT_INTERLEAVED = 0, LM_B200_ROT_HALF = 1 };
 /* FP32: every product is fp32 FMA arithmetic on the stored weights.  BF16: the products of a long step (a prompt portion)
  * run on the tensor cores with bf16 operands and fp32 accumulation; everything else stays fp32. */
 enum lm_b200_precision { LM_B200_PRECISION_FP32 = 0, LM_B200_PRECISION_BF16 = 1 };
 
-/* DYT: y = tanh(alpha x) w + b.  LAYER: y = (x - mean) / sqrt(var + eps) * w + b with the model's eps. */
+/* DYT: y = tanh(alpha x) w + b.  LAYER: y = (x - mean) / sqrt(var + eps) * w + b with the model's eps.
+ * RMS: y = x / sqrt(mean(x^2) + eps) * w (stream records, the final norm, the embedding norm). */
 typedef struct lm_b200_norm {
     const float *w, *b;
     float alpha;
@@ -132,6 +145,28 @@ typedef struct lm_b200_layer {
     int32_t router;                /* lm_b200_router_kind */
     const float *router_bias;      /* [experts] added to the router logits; NULL: none */
     float act_limit, shared_limit; /* clamps of a CLAMPED_GLU: routed experts / dense unit, shared expert */
+
+    /* ---- further mechanisms of the stream form (all zero / NULL where a record does not use them) ----
+     * w_in of the mixers below, in this order:
+     *   GATED_DELTA       q (kv_heads*dim) | k (kv_heads*dim) | v (heads*vdim) | beta (heads) | decay (heads) | gate (heads*vdim)
+     *   RETENTION         q (heads*dim) | k (heads*dim) | v (heads*vdim) | gate (heads*vdim)
+     *   LATENT_ATTENTION  query latent (q_rank) | key/value latent (kv_rank) | rotated key part (rot_dim) | gate (heads*vdim, unless GATE_NONE)
+     * GATED_DELTA uses conv_taps, conv_w, conv_tail, a_log [heads], dt_bias [heads], unit_eps, head_norm [vdim] and rec_state
+     * as CHANNEL_DELTA does; its decay is exp(-exp(a_log_h) softplus(z_h + dt_bias_h)) per head.  RETENTION: S <- head_decay_h S
+     * + k v^T with k times dim^-1/2 after its rotation, o = S^T q, o / rms(o) per head (head_norm NULL: no weight).
+     * FF_DENSE with ACT_RELU2: ws_gate_up holds the up rows alone [dense_ff][width]. */
+    int32_t parallel;              /* != 0: the feed-forward reads the streams as they were BEFORE the mixer's write; both outputs are written at once */
+    int32_t mixer_gate;            /* lm_b200_gate_kind */
+    int32_t rot_layout;            /* lm_b200_rot_layout (RETENTION, LATENT_ATTENTION; rot_dims / rot_freq as above) */
+    int32_t rot_dim;               /* LATENT_ATTENTION: every query head is [dim plain | rot_dim turned with the position]; ONE turned key part of
+                                      this size, shared by all heads, is cached behind the latent: latent_pages [pages][page_size][kv_rank + rot_dim],
+                                      w_uq [heads*(dim + rot_dim)][q_rank].  `window` > 0 limits its keys to the last `window` positions. */
+    const float *head_decay;       /* [heads] RETENTION */
+    int32_t identity_experts;      /* SOFTMAX_GROUPED: router outputs behind the `experts` real ones whose expert is the identity */
+    int32_t group_count, group_keep; /* groups of neighbouring router outputs (experts + identity_experts must divide); <= 1 group: no restriction */
+    float route_scale;             /* multiplies the normalised weights */
+    const float *route_correction; /* [experts + identity_experts] added to the scores for the choice only; NULL: none */
+    int32_t shared_gate;           /* != 0: w_router has one more row behind the router outputs, g; the shared unit's output is times sigmoid(g . h) */
 } lm_b200_layer;
 
 typedef struct lm_b200_model {
@@ -145,6 +180,7 @@ typedef struct lm_b200_model {
     int32_t step_graphs;           /* != 0: steps of a few rows (decoding) replay a CUDA graph captured at their first use */
     float logit_scale;             /* multiplies the logits (0 is read as 1) */
     float embed_scale;             /* multiplies the embedding rows (0 is read as 1) */
+    const float *embed_norm;       /* [width] RMS norm weight applied to the embedding rows (stream form); NULL: none */
 } lm_b200_model;
 
 typedef struct lm_b200_engine lm_b200_engine;
