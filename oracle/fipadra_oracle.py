@@ -217,9 +217,10 @@ def sub(w, prefix):
 MIXERS = {"delta": gated_delta, "latent_attention": latent_attention, "retention": retention}
 
 
-def forward(cfg: dict, w: dict, tokens, keep_layers: bool = False):
+def forward(cfg: dict, w: dict, tokens, keep_layers: bool = False, dtype=torch.float64):
     """Logits [T, vocab] of one whole sequence (and the residual stream after every layer)."""
     eps = cfg["norm"]["eps"]
+    w = {k: v.to(dtype) for k, v in w.items()}
     x = rms_unit(w["embed"][torch.as_tensor(tokens, dtype=torch.long)], eps) * w["embed.norm"]
     kept = []
     for i, lc in enumerate(cfg["layers"]):
@@ -239,3 +240,58 @@ def greedy(cfg: dict, w: dict, prompt, n_new: int):
     for _ in range(n_new):
         toks.append(int(forward(cfg, w, toks)[-1].argmax()))
     return toks[len(prompt):]
+
+
+def random_weights(cfg: dict, seed: int, spread: float = 1.0) -> dict:
+    """Random float32 tensors that bfloat16 holds exactly, under the checkpoint's names."""
+    g = torch.Generator().manual_seed(seed)
+    D, w = cfg["width"], {}
+
+    def mat(n_out, n_in, gain=1.0):
+        return (torch.randn((n_out, n_in), generator=g) * (gain * spread / math.sqrt(n_in))).to(torch.bfloat16).float()
+
+    def vec(n, mean=0.0, dev=0.1):
+        return (mean + dev * torch.randn((n,), generator=g)).to(torch.bfloat16).float()
+
+    def unit(prefix, ff):
+        w[prefix + "gate"], w[prefix + "up"], w[prefix + "down"] = mat(ff, D, 1.5), mat(ff, D, 1.5), mat(D, ff)
+
+    w["embed"] = (torch.randn((cfg["vocab"], D), generator=g) * spread).to(torch.bfloat16).float()
+    w["embed.norm"], w["final.norm"] = vec(D, 1.0), vec(D, 1.0)
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", lc["mixer"]
+        w[p + "norm1"] = vec(D, 1.0)
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        if lc["type"] == "delta":
+            G = m.get("kv_heads") or H
+            for name, n in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                w[p + "mix." + name] = mat(n, D, 1.5)
+                w[p + f"mix.{name}.conv"] = (torch.randn((n, m["conv"]), generator=g) * 0.7).to(torch.bfloat16).float()
+            w[p + "mix.b"], w[p + "mix.a"] = mat(H, D, 2.0), mat(H, D, 2.0)
+            w[p + "mix.A_log"], w[p + "mix.dt_bias"] = vec(H, -0.5, 0.7), vec(H, -1.0, 1.0)
+            w[p + "mix.norm"], w[p + "mix.g"] = vec(dv, 1.0), mat(H * dv, D, 1.5)
+        elif lc["type"] == "latent_attention":
+            dr = m.get("rot_dim", 0)
+            w[p + "mix.dq"], w[p + "mix.dq.norm"] = mat(m["q_rank"], D), vec(m["q_rank"], 1.0)
+            w[p + "mix.uq"] = mat(H * (d + dr), m["q_rank"], 2.0)
+            w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = mat(m["kv_rank"] + dr, D, 1.5), vec(m["kv_rank"], 1.0)
+            w[p + "mix.uk"], w[p + "mix.uv"] = mat(H * d, m["kv_rank"], 2.0), mat(H * dv, m["kv_rank"])
+        else:
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = mat(H * d, D, 1.5), mat(H * d, D, 1.5), mat(H * dv, D)
+            w[p + "mix.g"] = mat(H * dv, D, 1.5)
+        w[p + "mix.o"] = mat(D, H * dv)
+        f = lc.get("mlp")
+        if f:
+            w[p + "norm2"] = vec(D, 1.0)
+            if f["kind"] == "dense":
+                w[p + "mlp.up"], w[p + "mlp.down"] = mat(f["ff"], D, 1.5), mat(D, f["ff"])
+            else:
+                r = f["router"]
+                n = r["experts"] + r.get("identity", 0)
+                for e in range(r["experts"]):
+                    unit(p + f"mlp.e{e}.", f["expert"]["ff"])
+                w[p + "mlp.router"], w[p + "mlp.correction"] = mat(n, D, 3.0), vec(n, 0.0, 0.3 / n)
+                if f.get("shared"):
+                    unit(p + "mlp.shared.", f["shared"]["ff"])
+                    w[p + "mlp.shared.sg"] = mat(1, D, 2.0)
+    return w
