@@ -22,7 +22,8 @@ path); `value` is the sum over ranks divided by the slowest rank's time (weak sc
 `--lm` leaves that workload aside and measures the decoder-only language-model path (Pubopel, random weights) at layer
 sizes of a real model: prefill and decode throughput through `CausalLM`, and its GEMM / attention kernels beside Dia's
 at equal size (one JSON line, metric `lm_layer_throughput`).  `--lm --lm-design luketar` measures the Luketar design
-beside Kupelix and Pubopel at equal width and its mixers beside Kupelix's.  `--lm --lm-design kupelix` measures the Kupelix design
+beside Kupelix and Pubopel at equal width and its mixers beside Kupelix's.  `--lm --lm-design fipadra` measures the Fipadra
+design beside Luketar at equal width and its mixers beside their likes in Luketar and Kupelix.  `--lm --lm-design kupelix` measures the Kupelix design
 instead: its prefill and decode throughput beside Pubopel's at equal width, heads and vocabulary, its attention kernel
 beside Pubopel's on the same causal workload, and its recurrence kernels against the bytes and state updates they must move.
 """
@@ -943,6 +944,143 @@ def run_lm_luketar(args) -> None:
                       "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
 
 
+# ---- --lm --lm-design fipadra: the Fipadra design beside Luketar at equal width, its mixers beside their likes -----------------
+FIPADRA_SIZES = {
+    # the widths, head counts, latent sizes, expert sizes and vocabularies of LUKETAR_SIZES; a query / key head of 96 plain + 32
+    # turned channels (128 as there), a window as long as the decode context, a squared-relu unit with the parameter count of
+    # Luketar's gated one, two identity experts beside the eight / sixteen routed ones, two groups of which one is kept
+    "w2048": dict(width=2048, kinds=["delta", "latent_attention", "retention", "latent_attention"], heads=16, kv_heads=4, dim=128,
+                  vdim=128, q_rank=768, kv_rank=256, rot_dim=32, window=1024, taps=4, ff=6144, experts=8, top=2, identity=2,
+                  groups=(2, 1), expert_ff=2048, shared_ff=4096, vocab=32768),
+    "w1024": dict(width=1024, kinds=["delta", "latent_attention", "retention", "latent_attention"], heads=8, kv_heads=2, dim=128,
+                  vdim=128, q_rank=384, kv_rank=128, rot_dim=32, window=1024, taps=4, ff=1536, experts=16, top=2, identity=2,
+                  groups=(2, 1), expert_ff=512, shared_ff=1024, vocab=16384),
+}
+
+
+def _fipadra_config(sz: dict) -> dict:
+    """The model of a size entry: attention heads are [dim - rot_dim plain | rot_dim turned], the other mixers use `dim`."""
+    from dia_tts_prune_b200 import synthetic as SY
+    cfg = SY.fipadra_config(**sz)
+    for lc in cfg["layers"]:
+        if lc["type"] == "latent_attention":
+            lc["mixer"]["dim"] = sz["dim"] - sz["rot_dim"]
+    return cfg
+
+
+def run_lm_fipadra(args) -> None:
+    import torch
+    from dia_tts_prune_b200 import synthetic as SY
+    from dia_tts_prune_b200.lm_config import FipadraConfig, KupelixConfig, LuketarConfig
+    from dia_tts_prune_b200.lm_engine import launch_count
+    from dia_tts_prune_b200.lm_model import CausalLM
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        with open(os.path.join(REPO, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        hbm, tf, src = float(pk["hbm_gbs"]), float(pk["bf16_tflops"]), "measured"
+    except Exception:
+        hbm, tf, src = 6650.0, 1590.0, "fallback"
+    flush = torch.zeros(160 << 20, dtype=torch.uint8, device=dev)             # > the 126 MB L2
+    W, K = max(args.warmup, 3), max(args.steps, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    out = {}
+    T, ctx, R = args.lm_prompt, args.lm_context, args.lm_rows
+    for name in (args.lm_sizes.split(",") if args.lm_sizes else FIPADRA_SIZES):
+        sz, lsz, ksz = FIPADRA_SIZES[name], LUKETAR_SIZES[name], KUPELIX_SIZES[name]
+        D, H, G, d, dv, V = sz["width"], sz["heads"], sz["kv_heads"], sz["dim"], sz["vdim"], sz["vocab"]
+        rq, rk, dr, win = sz["q_rank"], sz["kv_rank"], sz["rot_dim"], sz["window"]
+        toks = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(7)).tolist()
+        cap = max(T, 8 * (ctx + 32 * (K + 2))) + 64
+        res = {"config": {k: (list(v) if isinstance(v, tuple) else v) for k, v in sz.items()}}
+        kw = dict(dtype="bfloat16", device=dev, max_tokens=cap, max_sequences=8, page_size=64, max_rows=R)
+        cfg = _fipadra_config(sz)
+        model = CausalLM(FipadraConfig.model_validate(cfg), SY.fipadra_weights(cfg, WEIGHT_SEED, dev), **kw)
+        res["fipadra"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        kinds = sz["kinds"]
+        # products per token and mixer: stacked input projections, (latent up-projections,) output projection
+        cols = {"delta": D * (2 * G * d + 2 * H * dv + 2 * H) + H * dv * D,
+                "retention": D * (2 * H * d + 2 * H * dv) + H * dv * D,
+                "latent_attention": D * (rq + rk + dr) + rq * H * d + H * (d - dr) * rk + H * rk * dv + H * dv * D}
+        moe_cols = 3 * D * (sz["top"] * sz["expert_ff"] + sz["shared_ff"]) + D * (sz["experts"] + sz["identity"] + 1)
+        ff_cols = [moe_cols if n % 2 else 2 * D * sz["ff"] for n in range(len(kinds))]
+        keys = sum(min(t + 1, win) for t in range(T))             # (query, key) pairs of a windowed prompt
+        mixer_flops = {"delta": 6.0 * T * H * d * dv, "retention": 4.0 * T * H * d * dv,
+                       "latent_attention": 2.0 * H * (2 * rk + dr) * keys}
+        flops = 2.0 * T * (sum(cols[k] for k in kinds) + sum(ff_cols)) + sum(mixer_flops[k] for k in kinds) + 2.0 * D * V
+        w_bytes = 2.0 * (sum(cols[k] for k in kinds) + sum(ff_cols) + D * V)
+        state = {"delta": 8.0 * H * d * dv, "retention": 8.0 * H * d * dv, "latent_attention": 4.0 * min(ctx, win) * (rk + dr)}
+        state_bytes = sum(state[k] for k in kinds) + 8.0 * len(kinds) * D
+        pf, b1 = res["fipadra"]["prefill"], res["fipadra"]["decode_b1"]
+        pf.update(model_tflops=flops / pf["ms"] / 1e9, frac_of_bf16_peak=flops / pf["ms"] / 1e9 / tf)
+        b1.update(algorithmic_bytes=w_bytes + state_bytes, gb_per_s=(w_bytes + state_bytes) / b1["ms_per_step"] / 1e6,
+                  frac_of_hbm_peak=(w_bytes + state_bytes) / b1["ms_per_step"] / 1e6 / hbm)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+        lcfg = SY.luketar_config(**lsz)
+        model = CausalLM(LuketarConfig.model_validate(lcfg), SY.luketar_weights(lcfg, WEIGHT_SEED, dev), **kw)
+        res["luketar"] = _lm_prefill_decode(model, toks, T, ctx, W, K, flush)
+        model.engine.close()
+        del model
+        torch.cuda.empty_cache()
+
+        # -- mixers alone (projections, kernels, output projection; no feed-forward): one-layer models of either design
+        def timed(m1, n_seq, rows_each, start):
+            h = torch.randn(n_seq * min(rows_each, R), D, device=dev)
+            seqs = [m1.state.open(f"s{i}") for i in range(n_seq)]
+            for sq in seqs:
+                m1.state.reserve(sq, start + rows_each)
+            def run():
+                for r0 in range(0, rows_each, R):
+                    n = min(R, rows_each - r0)
+                    m1.engine.op_mixer(0, h[:n_seq * n], [(sq, n, start + r0) for sq in seqs])
+            ms = _event_ms(run, 2, K, flush)
+            for i in range(n_seq):
+                m1.state.close(f"s{i}")
+            return ms
+
+        kw1 = dict(dtype="bfloat16", device=dev, max_tokens=8 * T + 64, max_sequences=8, page_size=64, max_rows=R)
+        mixers = {}
+        for kind, (twin_design, twin) in (("latent_attention", ("luketar", "latent_attention")), ("retention", ("luketar", "mlstm")),
+                                          ("delta", ("kupelix", "channel_delta"))):
+            c1 = _fipadra_config({**sz, "kinds": [kind], "vocab": 256, "ff": 0, "experts": 0})
+            m1 = CausalLM(FipadraConfig.model_validate(c1), SY.fipadra_weights(c1, 3, dev), **kw1)
+            if twin_design == "luketar":
+                c2 = SY.luketar_config(**{**lsz, "kinds": [twin], "vocab": 256, "ff": 0, "experts": 0, "streams": None})
+                m2 = CausalLM(LuketarConfig.model_validate(c2), SY.luketar_weights(c2, 3, dev), **kw1)
+            else:
+                c2 = SY.kupelix_config(**{**ksz, "kinds": [twin], "vocab": 256, "ff": 8})
+                m2 = CausalLM(KupelixConfig.model_validate(c2), SY.kupelix_weights(c2, 3, dev), **kw1)
+            ent = {}
+            for label, (n_seq, rows_each, start) in {"prefill_1x%d" % T: (1, T, 0), "prefill_8x%d" % (T // 8): (8, T // 8, 0),
+                                                     "decode_b8": (8, 1, ctx)}.items():
+                ent[label] = {"fipadra_ms": timed(m1, n_seq, rows_each, start),
+                              f"{twin_design}_{twin}_ms": timed(m2, n_seq, rows_each, start)}
+            if kind == "latent_attention":
+                ent["prefill_1x%d" % T].update(fipadra_attention_flops=2.0 * H * (2 * rk + dr) * keys,
+                                               luketar_attention_flops=4.0 * H * lsz["kv_rank"] * T * (T + 1) / 2)
+            mixers[kind] = ent
+            m1.engine.close()
+            m2.engine.close()
+            del m1, m2
+            torch.cuda.empty_cache()
+        res["mixers"] = mixers
+        out[name] = res
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "lm_layer_throughput", "design": "fipadra", "impl": "ours", "n_gpus": 1, "steps": K, "warmup": W,
+                      "dtype": "bf16", "data": "synthetic (random weights, random token ids)",
+                      "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src},
+                      "timing": "CUDA events, median; a 160 MB buffer is rewritten between timed iterations (L2 flush)",
+                      "gpu_launches": launch_count() - launches0, "clocks": clocks, "lm": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -965,16 +1103,17 @@ def main():
     ap.add_argument("--lm", action="store_true",
                     help="instead of the headline workload: prefill / decode throughput of the decoder-only language-model path "
                          "(Pubopel, random weights) at layer sizes of a real model, beside Dia's kernels at equal size")
-    ap.add_argument("--lm-design", default="pubopel", choices=["pubopel", "kupelix", "luketar"],
+    ap.add_argument("--lm-design", default="pubopel", choices=["pubopel", "kupelix", "luketar", "fipadra"],
                     help="--lm: the design that is measured (kupelix: beside Pubopel at equal width, and its kernels beside Pubopel's; "
-                         "luketar: beside Kupelix and Pubopel at equal width, and its mixers beside Kupelix's)")
+                         "luketar: beside Kupelix and Pubopel at equal width, and its mixers beside Kupelix's; fipadra: beside Luketar at equal "
+                         "width, and its mixers beside their likes in Luketar and Kupelix)")
     ap.add_argument("--lm-sizes", default="", help="--lm: comma-separated subset of " + ",".join(LM_SIZES))
     ap.add_argument("--lm-prompt", type=int, default=4096, help="--lm: prompt tokens of the prefill measurement")
     ap.add_argument("--lm-rows", type=int, default=4096, help="--lm: most rows of one engine step (longer prompts run in portions)")
     ap.add_argument("--lm-context", type=int, default=1024, help="--lm: tokens each sequence holds before the decode measurement")
     args = ap.parse_args()
     if args.lm:
-        {"kupelix": run_lm_kupelix, "luketar": run_lm_luketar}.get(args.lm_design, run_lm)(args)
+        {"kupelix": run_lm_kupelix, "luketar": run_lm_luketar, "fipadra": run_lm_fipadra}.get(args.lm_design, run_lm)(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -60,8 +60,12 @@ __device__ __forceinline__ float glu_act(int kind, float g, float u, float limit
 }
 
 // the kernels of a short step are launched with programmatic stream serialization (see pdl_release / pdl_wait)
+// early == false: a plain launch, which starts when its predecessor has ended.  For a kernel of few, long-running CTAs
+// behind a kernel of thousands of short ones (a recurrence scan behind its per-row preparation) that is the faster
+// order: CTAs that arrive while the predecessor drains are placed wherever a slot frees first, several to an SM, and
+// stay there for the whole scan.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+cudaError_t launch_pdl_if(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -71,8 +75,12 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = early ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    return launch_pdl_if(true, kernel, grid, block, smem, st, args...);
 }
 
 }  // namespace

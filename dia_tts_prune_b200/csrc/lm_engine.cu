@@ -494,7 +494,7 @@ int mixer_kernels(lm_b200_engine* e, const lm_b200_layer& l, const InCols& c, fl
             LCK(lm::launch_gate_prep(proj, c.n, c.q, c.f, c.v, l.in_bias, l.lower, l.heads * l.dim, l.heads * l.vdim, M, st));
             const lm::ScanInputs si{c.q, 0, c.f, c.v, 0};
             LCK(lm::launch_column_scan(proj, c.n, si, false, l.heads, l.heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
-                                       e->outcat, ko, st));
+                                       e->outcat, ko, st, false, M <= lm::kRowsKernelMax));
             LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, nullptr, 0, l.heads, l.vdim, e->m.eps, M, st));
             break;
         }
@@ -511,7 +511,7 @@ int mixer_kernels(lm_b200_engine* e, const lm_b200_layer& l, const InCols& c, fl
             LCK(lm::launch_conv_tail(proj, c.n, C, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
             const lm::ScanInputs si{0, k0, d0, v0, b0};
             LCK(lm::launch_column_scan(e->rec, ldr, si, true, l.heads, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq,
-                                       e->outcat, ko, st));
+                                       e->outcat, ko, st, false, M <= lm::kRowsKernelMax));
             LCK(lm::launch_head_norm_gate(e->outcat, ko, ob, l.head_norm, e->rec + g0, ldr, l.heads, l.vdim, e->m.eps, M, st));
             break;
         }
@@ -611,7 +611,7 @@ int stream_mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
         LCK(lm::launch_conv_tail(e->proj, c.n, v0 + nv, l.conv_taps, l.conv_tail, v.sm, n_seq, st));
         const lm::ScanInputs si{0, k0, d0, v0, b0};
         LCK(lm::launch_column_scan(e->rec, ldr, si, true, H, l.kv_heads, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq, e->att, nv, st,
-                                   true));
+                                   true, M <= lm::kRowsKernelMax));
         LCK(lm::launch_head_norm_gate(e->att, nv, bf ? e->attb : nullptr, l.head_norm, gate, c.n, H, l.vdim, e->m.eps, M, st, gate_act));
     } else if (l.mixer == LM_B200_MIXER_RETENTION) {
         // q and k (adjacent in the row) turn in place, k also takes dim^-1/2; decay fixed per head, no write gate, no normaliser
@@ -620,13 +620,13 @@ int stream_mixer(lm_b200_engine* e, const lm_b200_layer& l, const float* h, cons
                                 1.0f / sqrtf((float)l.dim), v.rm, M, st));
         const lm::ScanInputs si{c.q, c.k, 0, c.v, 0};
         LCK(lm::launch_scalar_gate_scan(e->proj, c.n, si, H, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq, e->att, nv, st,
-                                        l.head_decay, false));
+                                        l.head_decay, false, M <= lm::kRowsKernelMax));
         LCK(lm::launch_head_norm_gate(e->att, nv, bf ? e->attb : nullptr, l.head_norm, gate, c.n, H, l.vdim, e->m.eps, M, st, gate_act));
     } else {
         LCK(lm::launch_mlstm_gates(e->proj, c.n, c.ig, c.fg, l.in_bias, l.gate_cap, H, l.rec_aux, v.sm, v.rm, n_seq, e->floorb, st));
         const lm::ScanInputs si{c.q, c.k, c.fg, c.v, c.ig};      // decay in the forget column, write strength in the input column
         LCK(lm::launch_scalar_gate_scan(e->proj, c.n, si, H, l.dim, l.vdim, l.rec_state, v.sm, v.rm, n_seq, e->olat,
-                                        H * (l.vdim + 1), st));
+                                        H * (l.vdim + 1), st, nullptr, true, M <= lm::kRowsKernelMax));
         LCK(lm::launch_mlstm_finish(e->olat, H * (l.vdim + 1), e->floorb, 1.0f / sqrtf((float)l.dim), l.head_norm, e->proj + c.gate,
                                     c.n, e->m.eps, e->att, bf ? e->attb : nullptr, M, H, l.vdim, st));
     }

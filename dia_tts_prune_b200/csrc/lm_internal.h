@@ -119,16 +119,17 @@ cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* 
                              cudaStream_t st);
 cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_off, const float* bias, const float* lower, int n_qf,
                              int n_v, int M, cudaStream_t st);
+// early (both scans): launched so that it may start while its predecessor still runs (see launch_pdl_if)
 cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
                                float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
-                               cudaStream_t st, bool head_decay = false);
+                               cudaStream_t st, bool head_decay = false, bool early = true);
 // the same scan with scalar gates per (row, head): S <- a S + (b k) v^T and one more value column that is the constant 1
 // (the normaliser n <- a n + b k, read out as n . q), so state and read-out have vdim + 1 columns per head.  a and b are
 // columns a_off + h and beta_off + h of the input rows.  fixed_decay [H]: a = fixed_decay[h], b = 1 for every token instead.
 // normaliser false: no extra column (state and read-out have vdim columns per head).
 cudaError_t launch_scalar_gate_scan(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
                                     const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
-                                    const float* fixed_decay = nullptr, bool normaliser = true);
+                                    const float* fixed_decay = nullptr, bool normaliser = true, bool early = true);
 // gate_act: 0 the gate columns as they are, 1 their sigmoid, 2 their silu; w may be null (no weight)
 cudaError_t launch_head_norm_gate(float* o, int ldo, void* o_bf16, const float* w, const float* gate, int ldg, int H, int vdim,
                                   float eps, int M, cudaStream_t st, int gate_act = 0);

@@ -1072,13 +1072,13 @@ cudaError_t launch_conv_tail(const float* proj, int ld, int C, int taps, float* 
 template <int RP, bool DELTA>
 static cudaError_t launch_scan_inst(const float* in, int ld, const ScanInputs& si, int H, int G, int dim, int vdim, float* state,
                                     const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
-                                    bool head_decay) {
+                                    bool head_decay, bool early) {
     const size_t smem = (size_t)((DELTA ? 3 : 2) * kScanTT * 8 * RP + kScanTT * kScanCols + kScanTT) * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(column_scan_kernel<RP, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(column_scan_kernel<RP, DELTA>, dim3(n_seq, H, (vdim + kScanCols - 1) / kScanCols), dim3(kScanThreads), smem, st,
+    return launch_pdl_if(early, column_scan_kernel<RP, DELTA>, dim3(n_seq, H, (vdim + kScanCols - 1) / kScanCols), dim3(kScanThreads), smem, st,
                       in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, G, dim, vdim, state, sm.slot, sm.row0,
                       sm.count, rm.pos, o, ldo, head_decay ? 1 : 0);
 }
@@ -1091,11 +1091,11 @@ cudaError_t launch_gate_prep(float* proj, int ld, int q_off, int f_off, int v_of
 // delta: the delta rule (reads k and beta); otherwise the gate-tied write (its inputs prepared by launch_gate_prep)
 cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bool delta, int H, int G, int dim, int vdim,
                                float* state, const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo,
-                               cudaStream_t st, bool head_decay) {
+                               cudaStream_t st, bool head_decay, bool early) {
     if (dim > 256 || H % G || H > 65535) return cudaErrorNotSupported;
 #define SCAN_CASE(RP)                                                                                                    \
-    return delta ? launch_scan_inst<RP, true>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st, head_decay) \
-                 : launch_scan_inst<RP, false>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st, head_decay)
+    return delta ? launch_scan_inst<RP, true>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st, head_decay, early) \
+                 : launch_scan_inst<RP, false>(in, ld, si, H, G, dim, vdim, state, sm, rm, n_seq, o, ldo, st, head_decay, early)
     if (dim <= 32) SCAN_CASE(4);
     if (dim <= 64) SCAN_CASE(8);
     if (dim <= 128) SCAN_CASE(16);
@@ -1106,25 +1106,25 @@ cudaError_t launch_column_scan(const float* in, int ld, const ScanInputs& si, bo
 template <int RP>
 static cudaError_t launch_scalar_scan_inst(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
                                            const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
-                                           const float* fixed_decay, bool normaliser) {
+                                           const float* fixed_decay, bool normaliser, bool early) {
     const size_t smem = (size_t)(2 * kScanTT * 8 * RP + kScanTT * kScanCols + 2 * kScanTT) * 4;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(scalar_gate_scan_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(scalar_gate_scan_kernel<RP>, dim3(n_seq, H, (vdim + (normaliser ? 1 : 0) + kScanCols - 1) / kScanCols),
+    return launch_pdl_if(early, scalar_gate_scan_kernel<RP>, dim3(n_seq, H, (vdim + (normaliser ? 1 : 0) + kScanCols - 1) / kScanCols),
                       dim3(kScanThreads), smem, st, in, ld, si.q_off, si.k_off, si.a_off, si.v_off, si.beta_off, H, dim, vdim, state,
                       sm.slot, sm.row0, sm.count, rm.pos, o, ldo, fixed_decay, normaliser ? 1 : 0);
 }
 
 cudaError_t launch_scalar_gate_scan(const float* in, int ld, const ScanInputs& si, int H, int dim, int vdim, float* state,
                                     const SeqMeta& sm, const RowMeta& rm, int n_seq, float* o, int ldo, cudaStream_t st,
-                                    const float* fixed_decay, bool normaliser) {
+                                    const float* fixed_decay, bool normaliser, bool early) {
     if (dim > 256 || H > 65535) return cudaErrorNotSupported;
-    if (dim <= 32) return launch_scalar_scan_inst<4>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
-    if (dim <= 64) return launch_scalar_scan_inst<8>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
-    if (dim <= 128) return launch_scalar_scan_inst<16>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
-    return launch_scalar_scan_inst<32>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser);
+    if (dim <= 32) return launch_scalar_scan_inst<4>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser, early);
+    if (dim <= 64) return launch_scalar_scan_inst<8>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser, early);
+    if (dim <= 128) return launch_scalar_scan_inst<16>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser, early);
+    return launch_scalar_scan_inst<32>(in, ld, si, H, dim, vdim, state, sm, rm, n_seq, o, ldo, st, fixed_decay, normaliser, early);
 }
 
 cudaError_t launch_head_norm_gate(float* o, int ldo, void* o_bf16, const float* w, const float* gate, int ldg, int H, int vdim,

@@ -271,9 +271,12 @@ __global__ void __launch_bounds__(256)
 rot_rows_kernel(const float* __restrict__ src, int lds, int s_off, int shs, float* __restrict__ dst, int ldd, int d_off, int dhs,
                 int H, int n, int rot_dims, int half_layout, const float* __restrict__ freq, int split, float scale_a,
                 float scale_b, const int* __restrict__ row_pos) {
-    pdl_release();
+    extern __shared__ float trig[];                           // [rot_dims / 2] sines, then as many cosines: one pair of them per
+    pdl_release();                                            // turning pair of the row, shared by all heads
     pdl_wait();
     const int r = blockIdx.x, pos = row_pos[r], np = rot_dims >> 1, per = np + (n - rot_dims);   // items per head
+    for (int i = threadIdx.x; i < np; i += blockDim.x) sincosf((float)pos * freq[i], &trig[i], &trig[np + i]);
+    __syncthreads();
     const float* in = src + (size_t)r * lds + s_off;
     float* out = dst + (size_t)r * ldd + d_off;
     for (int idx = threadIdx.x; idx < H * per; idx += blockDim.x) {
@@ -283,10 +286,9 @@ rot_rows_kernel(const float* __restrict__ src, int lds, int s_off, int shs, floa
         float* oh = out + (size_t)h * dhs;
         if (it < np) {
             const int c0 = half_layout ? it : 2 * it, c1 = half_layout ? it + np : 2 * it + 1;
-            float a = ih[c0], b = ih[c1];
-            turn_pair(a, b, pos, freq[it]);
-            oh[c0] = a * sc;
-            oh[c1] = b * sc;
+            const float a = ih[c0], b = ih[c1], sn = trig[it], cs = trig[np + it];
+            oh[c0] = (a * cs - b * sn) * sc;
+            oh[c1] = (b * cs + a * sn) * sc;
         } else {
             const int c = rot_dims + (it - np);
             oh[c] = ih[c] * sc;
@@ -607,7 +609,7 @@ cudaError_t launch_latent_prep(float* proj, int ld, int q_off, int q_rank, int c
 cudaError_t launch_rot_rows(const float* src, int lds, int s_off, int shs, float* dst, int ldd, int d_off, int dhs, int H, int n,
                             const RotPart& rot, int split, float scale_a, float scale_b, const RowMeta& rm, int M, cudaStream_t st) {
     if (rot.dims < 0 || rot.dims % 2 || rot.dims > n || (rot.dims > 0 && !rot.freq)) return cudaErrorInvalidValue;
-    return launch_pdl(rot_rows_kernel, dim3(M), dim3(256), 0, st, src, lds, s_off, shs, dst, ldd, d_off, dhs, H, n, rot.dims,
+    return launch_pdl(rot_rows_kernel, dim3(M), dim3(256), (size_t)rot.dims * sizeof(float), st, src, lds, s_off, shs, dst, ldd, d_off, dhs, H, n, rot.dims,
                       rot.half_layout, rot.freq, split, scale_a, scale_b, rm.pos);
 }
 
