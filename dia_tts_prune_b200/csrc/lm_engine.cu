@@ -41,7 +41,21 @@
 //   y = out W_o^T                               linear
 //   feed-forward:     [gate | up] product, clamped activation, down product; routed experts grouped as above, their outputs
 //                     weighed by the softmax over the chosen logits inside the next streams_step
-// and after the last layer the streams are summed for the final norm.
+// and after the last layer the streams are summed for the final norm.  Norms of stream records are layer norms or RMS
+// norms (x / sqrt(mean(x^2) + eps) w), the embedding output may pass an RMS norm of its own, and three more mixers stand
+// beside the two above:
+//   gated delta rule: convolutions, silu, unit norms, beta and ONE decay per head (delta_prep); tails (conv_tail); the
+//                     recurrence (column_scan with a decay per head); per-head RMS norm x weight x silu(gate) (head_norm_gate)
+//   retention:        q | k turned in place, k x dim^-1/2 (rot_rows); S <- decay_h S + k v^T, o = S^T q (scalar_gate_scan with a
+//                     fixed decay, no normaliser); per-head RMS norm x silu(gate) (head_norm_gate)
+//   latent attention with a turned key part and a window: the cached row is [latent | turned key part]; the latent-space
+//                     query of a head is [q_plain^T W_uk | q_turned] (head_linear + rot_rows); the attention sees the last
+//                     `window` rows
+// A PARALLEL stream record lets both sublayers read the streams before either writes: the mixer's output waits in a buffer
+// of its own, and one streams_step writes both outputs (and, with one stream, gave both sublayers their inputs: two norm
+// weights on the same statistics).  The feed-forward may also be a dense squared-relu unit, and the mixture may route by
+// the softmax over all router outputs with a choice correction, groups, identity experts (they add weight x input inside
+// the next streams_step or down_combine_rows) and a sigmoid gate number on the shared unit (a column of the router logits).
 //
 // Products.  With float32 precision every product runs on the fp32 FMA kernels.  With bfloat16 precision a step of at
 // least kTensorRowsMin rows (a prompt portion) runs its products on the tensor cores (the tcgen05 kernel of

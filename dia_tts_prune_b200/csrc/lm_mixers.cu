@@ -23,8 +23,14 @@
 //                             S <- a S;  [u = beta (v - S^T k)];  S <- S + w u;  o = S^T q, state carried per sequence
 //   scalar_gate_scan_kernel   the same column layout for a recurrence with one decay and one write strength per token and
 //                             head, and a normaliser carried as one more value column
-//   head_norm_gate_kernel     per-head RMS norm of the read-out (x weight, x gate), fp32 in place and the bf16 operand
-//   xielu_rows_kernel         the dense feed-forward's activation on its slice of the stacked projections
+//                             (or a fixed decay per head, write strength 1, no normaliser: retention)
+//   head_norm_gate_kernel     per-head RMS norm of the read-out (x weight, x gate or its sigmoid / silu), fp32 in place and
+//                             the bf16 operand
+//   xielu_rows_kernel         the dense feed-forward's activation (xIELU or squared relu) on its slice of the stacked
+//                             projections
+// talk_attention_kernel also serves attention over cached latent rows (one key/value head whose value rows are the leading
+// channels of its key rows) and takes a window; delta_prep_kernel and column_scan_kernel also serve the delta rule with ONE
+// decay per head; layernorm_rows_kernel also computes the RMS norm.
 #include <algorithm>
 
 #include <cuda_bf16.h>

@@ -5,13 +5,20 @@
 // sequence state it points at, in an order of operations that does not depend on what else is in the batch.  The
 // streams, norms, latents, scores, gates, running maxima and the recurrent state are fp32.
 //
-//   streams_embed_kernel      token rows of a bf16 table times a constant, copied into every stream
+//   streams_embed_kernel      token rows of a bf16 table times a constant (optionally through an RMS norm), copied into every
+//                             stream
 //   streams_step_kernel       the write of one sublayer fused with the read of the next:  x_j <- sum_s mix[s][j] x_s +
 //                             out[j] y (y: the sublayer's output, with the weighted sum of a row's expert outputs added),
 //                             then u = sum_s in[s] x_s and h = layernorm(u) w, fp32 and the bf16 GEMM operand.  Without a
 //                             write it is the first read of a step; without in / w it is the plain sum of the streams
+//                             Options: a second output written with its own weights (a record whose sublayers read the same
+//                             streams), a second norm weight on the same statistics, RMS instead of layer norm, the input
+//                             row for assignments without a slot (identity experts), a sigmoid gate number on y
 //   latent_prep_kernel        RMS norms of the query latent (in place, + bf16 operand) and of the key/value latent (into
-//                             the pages: the latent is all an attention layer of this kind caches)
+//                             the pages: the latent is all an attention layer of this kind caches - and, behind it, one
+//                             key part turned with the position where the layer has one)
+//   rot_rows_kernel           rotary positions on a slice of every head of a row (pairs (2i, 2i + 1) or (i, i + dims / 2)),
+//                             with a multiplier per group of heads, in place or into another buffer
 //   latent_attention_rows_kernel  attention over the latent pages for shapes the tiled kernel does not take
 //   head_linear_*_kernel      per-head products Y[m][h] = alpha A[m][h] . W[h]^T with an optional sigmoid gate: queries
 //                             into the latent space (q_h^T W_uk,h) and attended latents out of it (W_uv,h o_h)

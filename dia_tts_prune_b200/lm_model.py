@@ -169,7 +169,7 @@ def build_fipadra_layers(cfg: FipadraConfig, w: dict[str, torch.Tensor], device)
                                    limit=f.expert.limit, shared_limit=f.shared.limit if f.shared is not None else None,
                                    softmax_all=True, identity=r.identity, correction=w.get(q + "correction"),
                                    groups=(r.groups.count, r.groups.keep) if r.groups is not None else None, route_scale=r.scale,
-                                   shared_gate=w[q + "shared.sg"] if f.shared is not None else None)
+                                   shared_gate=w.get(q + "shared.sg") if f.shared is not None else None)
         layers.append(StreamLayer(w[f"l{i}.norm1"], residual, mixer, ff, norm2, residual if ff is not None else None, device=device,
                                   parallel=True, rms=True))
     return layers, RmsNorm(w["final.norm"], device)
