@@ -157,7 +157,7 @@ typedef struct lm_b200_layer {
      * FF_DENSE with ACT_RELU2: ws_gate_up holds the up rows alone [dense_ff][width]. */
     int32_t parallel;              /* != 0: the feed-forward reads the streams as they were BEFORE the mixer's write; both outputs are written at once */
     int32_t mixer_gate;            /* lm_b200_gate_kind */
-    int32_t rot_layout;            /* lm_b200_rot_layout (RETENTION, LATENT_ATTENTION; rot_dims / rot_freq as above) */
+    int32_t rot_layout;            /* lm_b200_rot_layout; RETENTION and LATENT_ATTENTION, with rot_dims / rot_freq as above */
     int32_t rot_dim;               /* LATENT_ATTENTION: every query head is [dim plain | rot_dim turned with the position]; ONE turned key part of
                                       this size, shared by all heads, is cached behind the latent: latent_pages [pages][page_size][kv_rank + rot_dim],
                                       w_uq [heads*(dim + rot_dim)][q_rank].  `window` > 0 limits its keys to the last `window` positions. */
